@@ -118,7 +118,7 @@ __device__ __forceinline__ int quantize_q8_1_group8(float4 v, float &d16, float 
     return (q0 & 0xff) | ((q1 & 0xff) << 8) | ((q2 & 0xff) << 16) | (int)((unsigned)q3 << 24);
 }
 
-// ---------------------------------------------------------------- mbarrier + bulk async copy (TMA engine, SASS UBLKCP)
+// ---------------------------------------------------------------- mbarrier + bulk async copy (TMA engine)
 __device__ __forceinline__ void mbar_init(unsigned long long *bar, unsigned count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
 }

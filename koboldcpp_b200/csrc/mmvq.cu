@@ -8,7 +8,7 @@
 // B200 design (HBM-bound: the job is to keep >= ~40 KB of weight bytes in flight per SM and never touch a byte twice):
 //   * one persistent CTA per SM; CTA c owns a contiguous, byte-balanced range of the (concatenated) weight rows;
 //   * every warp streams whole rows through its OWN ring of shared-memory stages filled by the TMA engine with
-//     1-D bulk copies (cp.async.bulk ... mbarrier::complete_tx, SASS UBLKCP): the raw 144/176/210/34/18-byte blocks
+//     1-D bulk copies (cp.async.bulk ... mbarrier::complete_tx): the raw 144/176/210/34/18-byte blocks
 //     land in shared memory untouched, so no lane ever issues a misaligned or sub-32-bit global load, and no
 //     registers or LSU slots are spent on in-flight data.  Stage reuse is warp-private: no CTA barrier in the loop;
 //   * the f32 activation row(s) are quantised to q8_1 by the CTA itself while the first weight stages are in flight
