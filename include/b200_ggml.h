@@ -60,6 +60,7 @@ enum b200_type {
     B200_TYPE_IQ4_NL = 20,
     B200_TYPE_IQ4_XS = 23,
     B200_TYPE_I32  = 26,
+    B200_TYPE_BF16 = 30, /* dense weights of the float matmul (b200_op_mul_mat_float) */
 };
 
 B200_API const char *b200_last_error(void);

@@ -96,10 +96,95 @@ B200_API int b200_op_argsort(const b200_tensor *x, const b200_tensor *dst, int o
 /* SUM_ROWS: dst[row] = sum over ne0.  replaces k_sum_rows_f32, ggml-cuda/sumrows.cu:3-30 */
 B200_API int b200_op_sum_rows(const b200_tensor *x, const b200_tensor *dst, b200_stream_t stream);
 
-/* MUL_MAT with an f32 or f16 weight matrix (MoE router, small dense layers): dst[n][m] = sum_k W[m][k] X[n][k], with ggml's
+/* MUL_MAT with an f32, f16 or bf16 weight matrix (MoE router, small dense layers): dst[n][m] = sum_k W[m][k] X[n][k], with ggml's
  * broadcast over dims 2 and 3.  A bandwidth-oriented warp-per-output kernel; the quantised hot path lives in b200_ggml.h.
  * replaces the cuBLAS / mul_mat_vec_nc paths for float weights, ggml-cuda.cu:1042-1284 */
 B200_API int b200_op_mul_mat_float(const b200_tensor *w, const b200_tensor *x, const b200_tensor *dst, b200_stream_t stream);
+
+
+/* ------------------------------------------------------------------------------------------------------------------------
+ * Ops beyond the llama / mixtral graph (no counterpart in the reference): normalisation with a gate and a residual, a
+ * polynomial activation, rotation by a frequency table, a weighted sum over stacked activations, attention over a latent
+ * cache with a per-head sink, and a matrix-memory recurrence.  In a graph they travel as GGML_OP_MAP_CUSTOM1 nodes tagged
+ * B200_EXT_TAG in op_params[0] with the kind in op_params[1] (the tensor-parallel collectives use the same carrier).
+ * Everything here is computed in f32. */
+#define B200_EXT_TAG 0xB200E7A5u
+enum b200_ext_op {
+    B200_EXT_NORM = 1,         /* src: x, w, [gate, gate_bias, res]; op_params: [2] kind, [3] eps, [4] w_period */
+    B200_EXT_POLYNORM = 2,     /* src: x, coef[4]; op_params: [3] eps */
+    B200_EXT_ROPE_TABLE = 3,   /* src: x, pos, freqs; in place; op_params: [2] n_dims, [3] mscale, [4] neox */
+    B200_EXT_WEIGHTED_SUM = 4, /* src: xs [n, J], w [J] */
+    B200_EXT_SIGMOID_MUL = 5,  /* src: a, b: dst = a * sigmoid(b), any strides */
+    B200_EXT_LATENT_KV_STORE = 6, /* src: dkv, norm w, pos, freqs, cells, cache; op_params: [2] kv_rank, [3] eps, [4] mscale, [5] n_dims */
+    B200_EXT_LATENT_ATTN = 7,  /* src: q_lat, q_rot, cache, sink, tok_seq, tok_pos, cell_seq, cell_pos; op_params: [2] kv_rank, [3] scale, [4] window */
+    B200_EXT_MLSTM_SCAN = 8,   /* src: q, k, v, ig, fg, i_bias, f_bias, seq_info, state; op_params: [2] heads, [3] dim, [4] vdim, [5] gate_cap */
+};
+
+enum b200_norm_kind { B200_NORM_LAYER = 0 /* (x - mean) / sqrt(var + eps) */, B200_NORM_RMS = 1 /* x / sqrt(mean(x^2) + eps) */ };
+
+/* dst[row] = (res ? res[row] : 0) + N(x[row] * (gate ? sigmoid(gate[row] + gate_bias) : 1)) * w[(row % w_period)], N the layer
+ * norm or the RMS norm over ne0.  x, gate, res, dst: f32 rows (nb[0] == 4), any row strides; w: [w_period][ne0] f32 or NULL;
+ * gate_bias: [ne0] or NULL.  One block per row, statistics in f32 (variance = mean of squared deviations, two passes). */
+B200_API int b200_op_norm(const b200_tensor *x, const float *w, int64_t w_period, const b200_tensor *gate, const float *gate_bias,
+                          const b200_tensor *res, const b200_tensor *dst, float eps, int kind, b200_stream_t stream);
+
+/* PolyNorm: dst = c0 N(x) + c1 N(x^2) + c2 N(x^3) + c3 with N(z) = z / sqrt(mean(z^2) + eps) over ne0, powers element by
+ * element; coef: 4 floats on the device. */
+B200_API int b200_op_polynorm(const b200_tensor *x, const float *coef, const b200_tensor *dst, float eps, b200_stream_t stream);
+
+/* Rotation by a table of frequencies: for pair i < n_dims/2 of every row of x [ne0, ne1 (heads), ne2 (tokens)] the angle is
+ * pos[token] * freqs[i]; (u, v) -> mscale * (u cos - v sin, v cos + u sin).  Pairs are (2i, 2i+1), or (i, i + n_dims/2) with
+ * neox != 0; elements from n_dims on are copied.  x and dst may be the same view.  The table carries any frequency scaling
+ * (linear, NTK, YaRN ramps) computed once by the caller. */
+B200_API int b200_op_rope_table(const b200_tensor *x, const int32_t *pos, const float *freqs, const b200_tensor *dst, int32_t n_dims,
+                                int32_t neox, float mscale, b200_stream_t stream);
+
+/* dst[i] = sum_j w[j] * xs[j * slice_stride + i], j ascending, i < n. */
+B200_API int b200_op_weighted_sum(const float *xs, int64_t slice_stride, int32_t n_slices, const float *w, float *dst, int64_t n, b200_stream_t stream);
+
+/* dst = a * sigmoid(b); a, b, dst f32 of one shape with any strides (a permuted view is fine). */
+B200_API int b200_op_sigmoid_mul(const b200_tensor *a, const b200_tensor *b, const b200_tensor *dst, b200_stream_t stream);
+
+/* Latent KV cache (one row per cell: kv_rank normalised latent values, then rot_dim rotated key values, f32).
+ * store: row cells[t] = [ RMSnorm(dkv[t][:kv_rank]) * w , rope_table(dkv[t][kv_rank:]) ]. */
+B200_API int b200_op_latent_kv_store(const float *dkv, int64_t dkv_stride, const float *w, const int32_t *pos, const float *freqs, const int32_t *cells,
+                                     float *cache, int64_t cache_stride, int32_t kv_rank, int32_t rot_dim, int32_t n_dims, float mscale, float eps,
+                                     int32_t n_tokens, b200_stream_t stream);
+
+/* Attention of H query heads over the latent cache (every head reads the same rows: the key is the whole row, the value its
+ * first kv_rank entries).  score = scale * (q_lat . row[:kv_rank] + q_rot . row[kv_rank:]); a token sees the cells of its own
+ * sequence with cell_pos <= tok_pos (and cell_pos > tok_pos - window when window > 0); softmax in f32 whose denominator also
+ * holds exp(sink[h]) when sink != NULL.  Strides are in floats.  dst[h][t][:kv_rank] = sum_c p_c row_c[:kv_rank]. */
+typedef struct {
+    const float *q_lat; int64_t q_lat_s_head, q_lat_s_tok;
+    const float *q_rot; int64_t q_rot_s_head, q_rot_s_tok;
+    const float *cache; int64_t cache_stride;
+    const int32_t *cell_seq, *cell_pos, *tok_seq, *tok_pos;
+    const float *sink;
+    float *dst; int64_t dst_s_head, dst_s_tok;
+    int32_t kv_rank, rot_dim, n_head, n_tokens, n_kv, window;
+    float scale;
+} b200_latent_attn_args;
+B200_API int b200_op_latent_attn(const b200_latent_attn_args *a, b200_stream_t stream);
+
+/* Matrix-memory recurrence (mLSTM) over the tokens of n_seq sequences, state per (slot, head) in f32:
+ *   i = cap tanh((ig + i_bias) / cap),  f = logsigmoid(cap tanh((fg + f_bias) / cap)),  m' = max(f + m, i),
+ *   S' = exp(f + m - m') S + exp(i - m') k v^T,  n' likewise with k,  o = S'^T q / (max(|n' . q|, exp(-m')) + 1e-6),  q scaled by q_scale.
+ * seq_info: int32 [4][n_seq] = first token, token count, state slot, fresh (1: start from S = 0, n = 0, m = 0).
+ * State: slot_stride floats per slot, of which the first b200_mlstm_state_floats(heads, dim, vdim) are used: S [head][vdim][dim],
+ * then n and m once per column tile of the kernel (a tile never reads what another tile of the same launch writes).
+ * Strides in floats; dst [heads * vdim] per token. */
+B200_API int64_t b200_mlstm_state_floats(int32_t heads, int32_t dim, int32_t vdim);
+typedef struct {
+    const float *q, *k, *v, *ig, *fg; int64_t q_stride, k_stride, v_stride, g_stride;
+    const float *i_bias, *f_bias;
+    const int32_t *seq_info; int32_t n_seq;
+    float *state; int64_t slot_stride;
+    float *dst; int64_t dst_stride;
+    int32_t heads, dim, vdim;
+    float gate_cap, q_scale;
+} b200_mlstm_args;
+B200_API int b200_op_mlstm_scan(const b200_mlstm_args *a, b200_stream_t stream);
 
 #ifdef __cplusplus
 }

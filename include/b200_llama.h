@@ -37,7 +37,34 @@ typedef struct {
      * token_embd and the norm vectors are replicated.  The graph then holds n_head/W heads and n_head_kv/W KV heads per rank,
      * one all-reduce after attn_output and one after ffn_down, and an all-gather of the logits.  0 / 1 = off. */
     int32_t tp_rank, tp_world;
+    /* Architecture of the graph: 0 = llama / mixtral (everything above), else one of enum b200_arch.  Architectures whose layers
+     * differ from one another describe them with b200_llama_set_layer before the weights are uploaded; of the fields above they
+     * read n_embd, n_layer, n_vocab, n_ctx (cache cells, a multiple of 256), rms_eps (the eps of every norm) and main_device. */
+    int32_t arch;
+    int32_t n_seq_max;               /* sequences (and recurrent-state slots) that can be open at a time; 0 = 1 */
 } b200_llama_params;
+
+enum b200_arch { B200_ARCH_LLAMA = 0, B200_ARCH_GENESUN = 1 };
+enum b200_mixer { B200_MIXER_LATENT_ATTENTION = 1, B200_MIXER_MLSTM = 2 };
+enum b200_mlp { B200_MLP_NONE = 0, B200_MLP_DENSE_POLYNORM = 1 };
+
+/* One layer of an architecture with per-layer shapes (Genesun: config.json "layers"). */
+typedef struct {
+    int32_t mixer;                   /* enum b200_mixer */
+    int32_t heads, dim, vdim;        /* per head: (unrotated) query / key size and value size */
+    int32_t rot_dim, kv_rank, q_rank;/* latent attention: rotated size per head, latent sizes of keys / values and of queries */
+    int32_t kv_from;                 /* latent attention: layer whose cache this layer reads (-1: its own) */
+    int32_t window;                  /* attention window in tokens (0: every earlier token) */
+    float   scale;                   /* attention score scale */
+    int32_t rope_dims;               /* rotated dimensions (<= rot_dim) */
+    float   rope_base;
+    float   yarn_factor;             /* 0 or 1: no frequency scaling */
+    float   yarn_fast, yarn_slow;
+    int32_t yarn_original;
+    float   gate_cap;                /* mLSTM: soft cap of the gate pre-activations */
+    int32_t mlp, ff;                 /* enum b200_mlp and its hidden size */
+} b200_layer_params;
+
 
 typedef struct b200_llama b200_llama; /* opaque */
 
@@ -55,6 +82,21 @@ B200_API int b200_llama_clone_tensor(b200_llama *m, const char *name, const char
 
 /* Allocate KV cache + compute buffers once all weights are set (llama_new_context_with_model, src/llama.cpp:19507-19594). */
 B200_API int b200_llama_finalize(b200_llama *m, int32_t max_batch);
+
+/* Per-layer hyper-parameters (architectures other than llama), before any b200_llama_set_tensor. */
+B200_API int b200_llama_set_layer(b200_llama *m, int32_t il, const b200_layer_params *lp);
+
+/* Sequences: a batch step names the sequence of every token; the decoder keeps each sequence's cache cells, positions and
+ * recurrent state.  open returns a free sequence id (B200_ERR_NOMEM when n_seq_max are open); close gives its cells and its
+ * state slot back (llama_kv_cache_seq_rm over the whole sequence). */
+B200_API int b200_llama_seq_open(b200_llama *m, int32_t *seq_id);
+B200_API int b200_llama_seq_close(b200_llama *m, int32_t seq_id);
+B200_API int b200_llama_seq_length(b200_llama *m, int32_t seq_id);
+
+/* One step over a batch (llama_decode with a llama_batch of several sequences): tokens[i] continues sequence seq_ids[i] at that
+ * sequence's next position; the tokens of one sequence are adjacent and in order.  want[i] != 0 asks for the logits at token i;
+ * logits receives them in batch order, n_vocab floats each (want == NULL: none).  Synchronous on return. */
+B200_API int b200_llama_decode_batch(b200_llama *m, const int32_t *tokens, const int32_t *seq_ids, const int8_t *want, int32_t n_tokens, float *logits);
 
 /* Raw access to KV cells [cell0, cell0+n) of layer il (is_v: 0 = K, 1 = V): rows of n_embd_gqa values in type_k / type_v,
  * as llama_state_seq_set_data would write them (ggml_backend_tensor_set with an offset). */

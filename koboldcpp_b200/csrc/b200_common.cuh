@@ -34,13 +34,13 @@ constexpr int IQ4_NL_BYTES = 18;   // half d, u8 qs[16]: nibbles index 16 non-un
 constexpr int IQ4_XS_BYTES = 136;  // half d, u16 scales_h, u8 scales_l[4], u8 qs[128] (:413-418)
 
 __host__ __device__ constexpr int type_block_values(int t) {
-    return (t == B200_TYPE_F32 || t == B200_TYPE_F16 || t == B200_TYPE_I32) ? 1
+    return (t == B200_TYPE_F32 || t == B200_TYPE_F16 || t == B200_TYPE_I32 || t == B200_TYPE_BF16) ? 1
          : (t == B200_TYPE_Q4_0 || t == B200_TYPE_Q8_0 || t == B200_TYPE_Q8_1 || t == B200_TYPE_Q4_1 || t == B200_TYPE_Q5_0 || t == B200_TYPE_Q5_1 ||
             t == B200_TYPE_IQ4_NL) ? 32
          : (t == B200_TYPE_Q4_K || t == B200_TYPE_Q5_K || t == B200_TYPE_Q6_K || t == B200_TYPE_Q2_K || t == B200_TYPE_Q3_K || t == B200_TYPE_IQ4_XS) ? 256 : 0;
 }
 __host__ __device__ constexpr int type_block_bytes(int t) {
-    return t == B200_TYPE_F32 ? 4 : t == B200_TYPE_F16 ? 2 : t == B200_TYPE_I32 ? 4
+    return t == B200_TYPE_F32 ? 4 : t == B200_TYPE_F16 ? 2 : t == B200_TYPE_BF16 ? 2 : t == B200_TYPE_I32 ? 4
          : t == B200_TYPE_Q4_0 ? Q4_0_BYTES : t == B200_TYPE_Q8_0 ? Q8_0_BYTES : t == B200_TYPE_Q8_1 ? Q8_1_BYTES
          : t == B200_TYPE_Q4_1 ? Q4_1_BYTES : t == B200_TYPE_Q5_0 ? Q5_0_BYTES : t == B200_TYPE_Q5_1 ? Q5_1_BYTES
          : t == B200_TYPE_Q2_K ? Q2_K_BYTES : t == B200_TYPE_Q3_K ? Q3_K_BYTES

@@ -38,6 +38,115 @@ static bool mul_mat_q_bcast_ok(const ggml_tensor *w, const ggml_tensor *x, const
     return w->ne[0] == x->ne[0] && dst->ne[0] == w->ne[1] && dst->ne[1] == x->ne[1];
 }
 
+
+// ---- extension ops (GGML_OP_MAP_CUSTOM1 tagged B200_EXT_TAG; operands per kind: include/b200_ggml_ops.h, enum b200_ext_op)
+static float ext_f(const ggml_tensor *n, int i) { float v; memcpy(&v, n->op_params + i, 4); return v; }
+static bool f32_rows(const ggml_tensor *t) { return t && t->type == GGML_TYPE_F32 && t->nb[0] == 4; }
+static bool i32_vec(const ggml_tensor *t) { return t && t->type == GGML_TYPE_I32 && t->nb[0] == 4; }
+static bool f32_vec(const ggml_tensor *t) { return t && t->type == GGML_TYPE_F32 && is_contiguous(t); }
+
+static bool ext_op_supported(const ggml_tensor *op) {
+    const ggml_tensor *const *s = op->src;
+    switch (op->op_params[1]) {
+        case B200_EXT_NORM:
+            return f32_rows(s[0]) && f32_rows(op) && same_shape(s[0], op) && (!s[1] || f32_vec(s[1])) && (!s[2] || (f32_rows(s[2]) && same_shape(s[2], op))) &&
+                   (!s[3] || f32_vec(s[3])) && (!s[4] || (f32_rows(s[4]) && same_shape(s[4], op)));
+        case B200_EXT_POLYNORM:
+            return f32_rows(s[0]) && f32_rows(op) && same_shape(s[0], op) && f32_vec(s[1]) && nelements(s[1]) == 4;
+        case B200_EXT_ROPE_TABLE:
+            return f32_rows(s[0]) && f32_rows(op) && same_shape(s[0], op) && i32_vec(s[1]) && f32_vec(s[2]) && s[0]->ne[3] == 1 && s[1]->ne[0] >= s[0]->ne[2];
+        case B200_EXT_WEIGHTED_SUM:
+            return f32_rows(s[0]) && f32_vec(s[1]) && is_contiguous(op) && op->type == GGML_TYPE_F32 && s[1]->ne[0] == s[0]->ne[2] && s[0]->nb[1] == 4 * (size_t)s[0]->ne[0] &&
+                   nelements(op) == s[0]->ne[0] * s[0]->ne[1];
+        case B200_EXT_SIGMOID_MUL:
+            return s[0] && s[1] && s[0]->type == GGML_TYPE_F32 && s[1]->type == GGML_TYPE_F32 && op->type == GGML_TYPE_F32 && same_shape(s[0], op) && same_shape(s[1], op);
+        case B200_EXT_LATENT_KV_STORE:
+            return f32_rows(s[0]) && f32_vec(s[1]) && i32_vec(s[2]) && f32_vec(s[3]) && i32_vec(s[4]) && f32_rows(s[5]) && op->op_params[2] > 0 &&
+                   s[0]->ne[0] == s[5]->ne[0] && op->op_params[2] <= s[0]->ne[0];
+        case B200_EXT_LATENT_ATTN:
+            return f32_rows(s[0]) && (!s[1] || f32_rows(s[1])) && f32_rows(s[2]) && (!s[3] || f32_vec(s[3])) && i32_vec(s[4]) && i32_vec(s[5]) && i32_vec(s[6]) && i32_vec(s[7]) &&
+                   f32_rows(op) && op->op_params[2] == s[0]->ne[0] && op->ne[0] == s[0]->ne[0] && s[0]->ne[0] <= 1024 && s[2]->ne[0] - s[0]->ne[0] <= 128;
+        case B200_EXT_MLSTM_SCAN:
+            for (int i = 0; i < 5; i++) if (!f32_rows(s[i])) return false;
+            return (!s[5] || f32_vec(s[5])) && (!s[6] || f32_vec(s[6])) && i32_vec(s[7]) && f32_rows(s[8]) && f32_rows(op) && op->op_params[3] <= 512;
+        default:
+            return false;
+    }
+}
+
+static void run_ext(ExecCtx &x, const ggml_tensor *n) {
+    const ggml_tensor *const *s = n->src;
+    switch (n->op_params[1]) {
+        case B200_EXT_NORM: {
+            b200_tensor a = as_b200(s[0]), d = as_b200(n), g, r;
+            if (s[2]) g = as_b200(s[2]);
+            if (s[4]) r = as_b200(s[4]);
+            B200_CHECK_RC(b200_op_norm(&a, s[1] ? (const float *)s[1]->data : nullptr, n->op_params[4], s[2] ? &g : nullptr, s[3] ? (const float *)s[3]->data : nullptr,
+                                       s[4] ? &r : nullptr, &d, ext_f(n, 3), n->op_params[2], x.stream));
+            break;
+        }
+        case B200_EXT_POLYNORM: {
+            b200_tensor a = as_b200(s[0]), d = as_b200(n);
+            B200_CHECK_RC(b200_op_polynorm(&a, (const float *)s[1]->data, &d, ext_f(n, 3), x.stream));
+            break;
+        }
+        case B200_EXT_ROPE_TABLE: {
+            b200_tensor a = as_b200(s[0]), d = as_b200(n);
+            B200_CHECK_RC(b200_op_rope_table(&a, (const int32_t *)s[1]->data, (const float *)s[2]->data, &d, n->op_params[2], n->op_params[4], ext_f(n, 3), x.stream));
+            break;
+        }
+        case B200_EXT_WEIGHTED_SUM:
+            B200_CHECK_RC(b200_op_weighted_sum((const float *)s[0]->data, (int64_t)(s[0]->nb[2] / 4), (int32_t)s[0]->ne[2], (const float *)s[1]->data, (float *)n->data,
+                                               nelements(n), x.stream));
+            break;
+        case B200_EXT_SIGMOID_MUL: {
+            b200_tensor a = as_b200(s[0]), b = as_b200(s[1]), d = as_b200(n);
+            B200_CHECK_RC(b200_op_sigmoid_mul(&a, &b, &d, x.stream));
+            break;
+        }
+        case B200_EXT_LATENT_KV_STORE: {
+            const int32_t kv_rank = n->op_params[2];
+            B200_CHECK_RC(b200_op_latent_kv_store((const float *)s[0]->data, (int64_t)(s[0]->nb[1] / 4), (const float *)s[1]->data, (const int32_t *)s[2]->data,
+                                                  (const float *)s[3]->data, (const int32_t *)s[4]->data, (float *)s[5]->data, (int64_t)(s[5]->nb[1] / 4), kv_rank,
+                                                  (int32_t)s[0]->ne[0] - kv_rank, n->op_params[5], ext_f(n, 4), ext_f(n, 3), (int32_t)s[0]->ne[1], x.stream));
+            break;
+        }
+        case B200_EXT_LATENT_ATTN: {
+            // q_lat [kv_rank, heads, tokens] and q_rot [rot_dim, heads, tokens] (any strides); dst [kv_rank, tokens, heads]
+            b200_latent_attn_args a;
+            memset(&a, 0, sizeof(a));
+            a.q_lat = (const float *)s[0]->data; a.q_lat_s_head = (int64_t)(s[0]->nb[1] / 4); a.q_lat_s_tok = (int64_t)(s[0]->nb[2] / 4);
+            if (s[1]) { a.q_rot = (const float *)s[1]->data; a.q_rot_s_head = (int64_t)(s[1]->nb[1] / 4); a.q_rot_s_tok = (int64_t)(s[1]->nb[2] / 4); }
+            a.cache = (const float *)s[2]->data; a.cache_stride = (int64_t)(s[2]->nb[1] / 4);
+            a.sink = s[3] ? (const float *)s[3]->data : nullptr;
+            a.tok_seq = (const int32_t *)s[4]->data; a.tok_pos = (const int32_t *)s[5]->data;
+            a.cell_seq = (const int32_t *)s[6]->data; a.cell_pos = (const int32_t *)s[7]->data;
+            a.dst = (float *)n->data; a.dst_s_tok = (int64_t)(n->nb[1] / 4); a.dst_s_head = (int64_t)(n->nb[2] / 4);
+            a.kv_rank = n->op_params[2]; a.rot_dim = (int32_t)s[2]->ne[0] - a.kv_rank; a.n_head = (int32_t)s[0]->ne[1]; a.n_tokens = (int32_t)s[0]->ne[2];
+            a.n_kv = (int32_t)s[6]->ne[0]; a.window = n->op_params[4]; a.scale = ext_f(n, 3);
+            B200_CHECK_RC(b200_op_latent_attn(&a, x.stream));
+            break;
+        }
+        case B200_EXT_MLSTM_SCAN: {
+            b200_mlstm_args a;
+            memset(&a, 0, sizeof(a));
+            a.q = (const float *)s[0]->data; a.q_stride = (int64_t)(s[0]->nb[1] / 4);
+            a.k = (const float *)s[1]->data; a.k_stride = (int64_t)(s[1]->nb[1] / 4);
+            a.v = (const float *)s[2]->data; a.v_stride = (int64_t)(s[2]->nb[1] / 4);
+            a.ig = (const float *)s[3]->data; a.fg = (const float *)s[4]->data; a.g_stride = (int64_t)(s[3]->nb[1] / 4);
+            a.i_bias = s[5] ? (const float *)s[5]->data : nullptr; a.f_bias = s[6] ? (const float *)s[6]->data : nullptr;
+            a.seq_info = (const int32_t *)s[7]->data; a.n_seq = (int32_t)s[7]->ne[0];
+            a.state = (float *)s[8]->data; a.slot_stride = (int64_t)(s[8]->nb[1] / 4);
+            a.dst = (float *)n->data; a.dst_stride = (int64_t)(n->nb[1] / 4);
+            a.heads = n->op_params[2]; a.dim = n->op_params[3]; a.vdim = n->op_params[4]; a.gate_cap = ext_f(n, 5); a.q_scale = ext_f(n, 6);
+            B200_CHECK_RC(b200_op_mlstm_scan(&a, x.stream));
+            break;
+        }
+        default:
+            backend_abort("graph_compute", "unknown extension op");
+    }
+}
+
 bool op_supported(int /*device*/, const ggml_tensor *op) {
     const ggml_tensor *s0 = op->src[0], *s1 = op->src[1];
     for (int i = 0; i < GGML_MAX_SRC; i++) {
@@ -47,7 +156,8 @@ bool op_supported(int /*device*/, const ggml_tensor *op) {
     switch (op->op) {
         case GGML_OP_NONE: case GGML_OP_RESHAPE: case GGML_OP_VIEW: case GGML_OP_PERMUTE: case GGML_OP_TRANSPOSE:
             return true;
-        case GGML_OP_MAP_CUSTOM1:  // a collective of the tensor-parallel decoder (b200_comm.h)
+        case GGML_OP_MAP_CUSTOM1:  // an extension op (b200_ggml_ops.h) or a collective of the tensor-parallel decoder (b200_comm.h)
+            if ((uint32_t)op->op_params[0] == B200_EXT_TAG) return ext_op_supported(op);
             if (!s0 || (uint32_t)op->op_params[0] != B200_COLLECTIVE_TAG || b200_comm_world() < 1) return false;
             if (s0->type != GGML_TYPE_F32 || op->type != GGML_TYPE_F32 || !is_contiguous(s0) || !is_contiguous(op)) return false;
             if (op->op_params[1] == B200_COLLECTIVE_ALL_REDUCE_SUM) return nelements(op) == nelements(s0);
@@ -56,7 +166,7 @@ bool op_supported(int /*device*/, const ggml_tensor *op) {
         case GGML_OP_MUL_MAT:
             if (!s0 || !s1) return false;
             if (is_quantized(s0->type)) return mul_mat_q_ok(s0, s1, op) || mul_mat_q_bcast_ok(s0, s1, op);
-            return (s0->type == GGML_TYPE_F32 || s0->type == GGML_TYPE_F16) && s1->type == GGML_TYPE_F32 && op->type == GGML_TYPE_F32 &&
+            return (s0->type == GGML_TYPE_F32 || s0->type == GGML_TYPE_F16 || s0->type == GGML_TYPE_BF16) && s1->type == GGML_TYPE_F32 && op->type == GGML_TYPE_F32 &&
                    s0->nb[0] == (size_t)type_traits(s0->type).size && s1->nb[0] == 4 && !in_split_buffer(s0);
         case GGML_OP_MUL_MAT_ID: {
             const ggml_tensor *ids = op->src[2];
@@ -358,6 +468,7 @@ void run_node(ExecCtx &x, const ggml_tensor *n, void *const *dst_slot) {
         case GGML_OP_NONE: case GGML_OP_RESHAPE: case GGML_OP_VIEW: case GGML_OP_PERMUTE: case GGML_OP_TRANSPOSE:
             return;
         case GGML_OP_MAP_CUSTOM1: {
+            if ((uint32_t)n->op_params[0] == B200_EXT_TAG) { run_ext(x, n); break; }
             if (n->op_params[1] == B200_COLLECTIVE_ALL_REDUCE_SUM) {
                 if (peer_all_reduce_ok(n)) {  // decode-size message: one kernel over NVLink peer memory (comm.cu)
                     B200_CHECK_RC(b200_all_reduce_sum_add_f32((const float *)s0->data, nullptr, (float *)n->data, nelements(n), x.stream));

@@ -4,320 +4,21 @@
 // constructors below fill struct ggml_tensor the way the ggml_* builders do (ggml.c: ggml_new_tensor_impl :3790-3870,
 // ggml_view_impl :6130-6190, ggml_permute :6300-6350, ggml_rope_impl :6920-6975, ggml_flash_attn_ext :7130-7180, ...).
 // No compute happens in this file.
-#include <chrono>
-#include <cmath>
-#include <deque>
-#include <map>
-#include <unordered_set>
+#include "host_model.h"
 
-#include "../../include/b200_comm.h"
-#include "../../include/b200_llama.h"
-#include "backend_internal.h"
-
-namespace b200 {
-void set_error(const char *fmt, ...);
-}
-using namespace b200;
-
-namespace {
-
-const int KV_PAD = 256;  // llama_kv_cache_get_padding with flash attention, src/llama.cpp:4143-4146
-
-// ------------------------------------------------------------------------------------------------ tensor arena
-struct Arena {
-    std::deque<ggml_tensor> pool;  // stable addresses
-    size_t used = 0;
-    void reset() { used = 0; }
-    ggml_tensor *get() {
-        if (used == pool.size()) pool.emplace_back();
-        ggml_tensor *t = &pool[used++];
-        memset(t, 0, sizeof(*t));
-        return t;
-    }
-};
-
-void set_shape(ggml_tensor *t, int type, int64_t ne0, int64_t ne1, int64_t ne2, int64_t ne3) {
-    const TypeTraits tt = type_traits(type);
-    t->type = (ggml_type)type;
-    t->ne[0] = ne0; t->ne[1] = ne1; t->ne[2] = ne2; t->ne[3] = ne3;
-    t->nb[0] = (size_t)tt.size;
-    t->nb[1] = t->nb[0] * (size_t)(ne0 / tt.blck);
-    t->nb[2] = t->nb[1] * (size_t)ne1;
-    t->nb[3] = t->nb[2] * (size_t)ne2;
-}
-
-// bump allocator over one backend buffer (stands in for ggml-alloc: every graph gets the same addresses again)
-struct Bump {
-    ggml_backend_buffer_t buf = nullptr;
-    char *base = nullptr;
-    size_t size = 0, off = 0, align = 128;
-    void *take(size_t bytes) {
-        off = (off + align - 1) / align * align;
-        if (off + bytes > size) return nullptr;
-        void *p = base + off;
-        off += bytes;
-        return p;
-    }
-};
-
-struct Builder {
-    Arena *arena;
-    Bump *bump;
-    std::vector<ggml_tensor *> nodes;
-    std::unordered_set<const ggml_tensor *> visited;
-    bool oom = false;
-
-    // ggml_build_forward_expand: post-order DFS over src[], left to right (ggml_visit_parents, ggml.c:19020-19070);
-    // tensors with op NONE are leafs and not part of the node list
-    void expand(ggml_tensor *t) {
-        if (!t || !visited.insert(t).second) return;
-        for (int i = 0; i < GGML_MAX_SRC; i++) expand(t->src[i]);
-        if (t->op != GGML_OP_NONE) nodes.push_back(t);
-    }
-
-    ggml_tensor *alloc_result(int type, int64_t ne0, int64_t ne1 = 1, int64_t ne2 = 1, int64_t ne3 = 1) {
-        ggml_tensor *t = arena->get();
-        set_shape(t, type, ne0, ne1, ne2, ne3);
-        t->data = bump->take(nbytes(t));
-        if (!t->data) oom = true;
-        t->buffer = bump->buf;
-        return t;
-    }
-    ggml_tensor *op(ggml_tensor *t, int o, ggml_tensor *a, ggml_tensor *b = nullptr, ggml_tensor *c = nullptr, ggml_tensor *d = nullptr) {
-        t->op = (ggml_op)o;
-        t->src[0] = a; t->src[1] = b; t->src[2] = c; t->src[3] = d;
-        return t;
-    }
-    // views share the data of their source (ggml_view_impl)
-    ggml_tensor *view_of(ggml_tensor *a, int o, size_t offs) {
-        ggml_tensor *t = arena->get();
-        t->type = a->type;
-        t->buffer = a->buffer;
-        t->view_src = a->view_src ? a->view_src : a;
-        t->view_offs = (a->view_src ? a->view_offs : 0) + offs;
-        t->data = a->data ? (char *)a->data + offs : nullptr;
-        t->op = (ggml_op)o;
-        t->src[0] = a;
-        return t;
-    }
-    ggml_tensor *reshape(ggml_tensor *a, int64_t ne0, int64_t ne1 = 1, int64_t ne2 = 1, int64_t ne3 = 1) {
-        ggml_tensor *t = view_of(a, GGML_OP_RESHAPE, 0);
-        set_shape(t, a->type, ne0, ne1, ne2, ne3);
-        return t;
-    }
-    ggml_tensor *view_1d(ggml_tensor *a, int64_t ne0, size_t offs) {
-        ggml_tensor *t = view_of(a, GGML_OP_VIEW, offs);
-        set_shape(t, a->type, ne0, 1, 1, 1);
-        memcpy(t->op_params, &offs, sizeof(offs));
-        return t;
-    }
-    ggml_tensor *view_2d(ggml_tensor *a, int64_t ne0, int64_t ne1, size_t nb1, size_t offs) {
-        ggml_tensor *t = view_of(a, GGML_OP_VIEW, offs);
-        set_shape(t, a->type, ne0, ne1, 1, 1);
-        t->nb[1] = nb1; t->nb[2] = nb1 * (size_t)ne1; t->nb[3] = t->nb[2];
-        memcpy(t->op_params, &offs, sizeof(offs));
-        return t;
-    }
-    ggml_tensor *view_3d(ggml_tensor *a, int64_t ne0, int64_t ne1, int64_t ne2, size_t nb1, size_t nb2, size_t offs) {
-        ggml_tensor *t = view_of(a, GGML_OP_VIEW, offs);
-        set_shape(t, a->type, ne0, ne1, ne2, 1);
-        t->nb[1] = nb1; t->nb[2] = nb2; t->nb[3] = nb2 * (size_t)ne2;
-        memcpy(t->op_params, &offs, sizeof(offs));
-        return t;
-    }
-    ggml_tensor *permute(ggml_tensor *a, int ax0, int ax1, int ax2, int ax3) {
-        ggml_tensor *t = view_of(a, GGML_OP_PERMUTE, 0);
-        const int ax[4] = {ax0, ax1, ax2, ax3};
-        for (int i = 0; i < 4; i++) { t->ne[ax[i]] = a->ne[i]; t->nb[ax[i]] = a->nb[i]; }
-        for (int i = 0; i < 4; i++) t->op_params[i] = ax[i];
-        return t;
-    }
-    ggml_tensor *rms_norm(ggml_tensor *a, float eps) {
-        ggml_tensor *t = alloc_result(GGML_TYPE_F32, a->ne[0], a->ne[1], a->ne[2], a->ne[3]);
-        memcpy(t->op_params, &eps, 4);
-        return op(t, GGML_OP_RMS_NORM, a);
-    }
-    ggml_tensor *binary(int o, ggml_tensor *a, ggml_tensor *b) {
-        return op(alloc_result(GGML_TYPE_F32, a->ne[0], a->ne[1], a->ne[2], a->ne[3]), o, a, b);
-    }
-    ggml_tensor *mul_mat(ggml_tensor *w, ggml_tensor *x) {
-        return op(alloc_result(GGML_TYPE_F32, w->ne[1], x->ne[1], x->ne[2], x->ne[3]), GGML_OP_MUL_MAT, w, x);
-    }
-    // as [K, M, n_expert], b [K, n_b_rows, T], ids [n_used, T] -> [M, n_used, T]   (ggml.c:5693-5729)
-    ggml_tensor *mul_mat_id(ggml_tensor *as, ggml_tensor *b, ggml_tensor *ids) {
-        return op(alloc_result(GGML_TYPE_F32, as->ne[1], ids->ne[0], b->ne[2], 1), GGML_OP_MUL_MAT_ID, as, b, ids);
-    }
-    ggml_tensor *rope(ggml_tensor *a, ggml_tensor *pos, ggml_tensor *ff, int n_dims, int mode, int n_ctx_orig, float freq_base, float freq_scale) {
-        ggml_tensor *t = alloc_result(GGML_TYPE_F32, a->ne[0], a->ne[1], a->ne[2], a->ne[3]);
-        const float ext_factor = 0.0f, attn_factor = 1.0f, beta_fast = 32.0f, beta_slow = 1.0f;  // llama_context_default_params
-        int32_t p[11] = {0, n_dims, mode, 0, n_ctx_orig};
-        memcpy(p + 5, &freq_base, 4); memcpy(p + 6, &freq_scale, 4); memcpy(p + 7, &ext_factor, 4);
-        memcpy(p + 8, &attn_factor, 4); memcpy(p + 9, &beta_fast, 4); memcpy(p + 10, &beta_slow, 4);
-        memcpy(t->op_params, p, sizeof(p));
-        return op(t, GGML_OP_ROPE, a, pos, ff);
-    }
-    // CPY(a, b): the result is a view of b (ggml_cpy_impl, ggml.c:5982-6005)
-    ggml_tensor *cpy(ggml_tensor *a, ggml_tensor *b) {
-        ggml_tensor *t = arena->get();
-        *t = *b;
-        t->view_src = b->view_src ? b->view_src : b;
-        t->view_offs = b->view_src ? b->view_offs : 0;
-        memset(t->op_params, 0, sizeof(t->op_params));
-        memset(t->src, 0, sizeof(t->src));
-        return op(t, GGML_OP_CPY, a, b);
-    }
-    ggml_tensor *cast(ggml_tensor *a, int type) {  // ggml_cast: CPY into a fresh tensor of `type`
-        ggml_tensor *t = alloc_result(type, a->ne[0], a->ne[1], a->ne[2], a->ne[3]);
-        return op(t, GGML_OP_CPY, a, t);
-    }
-    ggml_tensor *get_rows(ggml_tensor *a, ggml_tensor *ids) {
-        return op(alloc_result(GGML_TYPE_F32, a->ne[0], ids->ne[0], ids->ne[1], 1), GGML_OP_GET_ROWS, a, ids);
-    }
-    ggml_tensor *flash_attn(ggml_tensor *q, ggml_tensor *k, ggml_tensor *v, ggml_tensor *mask, float scale) {
-        // result [D, n_head, N] (ggml.c:7165: ne = { v->ne[0], q->ne[2], q->ne[1], q->ne[3] })
-        ggml_tensor *t = alloc_result(GGML_TYPE_F32, v->ne[0], q->ne[2], q->ne[1], q->ne[3]);
-        const float p[3] = {scale, 0.0f, 0.0f};
-        memcpy(t->op_params, p, sizeof(p));
-        return op(t, GGML_OP_FLASH_ATTN_EXT, q, k, v, mask);
-    }
-    ggml_tensor *silu(ggml_tensor *a) {
-        ggml_tensor *t = alloc_result(GGML_TYPE_F32, a->ne[0], a->ne[1], a->ne[2], a->ne[3]);
-        t->op_params[0] = GGML_UNARY_OP_SILU;
-        return op(t, GGML_OP_UNARY, a);
-    }
-    ggml_tensor *soft_max(ggml_tensor *a) {
-        ggml_tensor *t = alloc_result(GGML_TYPE_F32, a->ne[0], a->ne[1], a->ne[2], a->ne[3]);
-        const float p[2] = {1.0f, 0.0f};
-        memcpy(t->op_params, p, sizeof(p));
-        return op(t, GGML_OP_SOFT_MAX, a);
-    }
-    ggml_tensor *top_k(ggml_tensor *a, int k) {  // ggml_top_k = argsort(desc) + view (ggml.c:7080-7095)
-        ggml_tensor *s = alloc_result(GGML_TYPE_I32, a->ne[0], a->ne[1], a->ne[2], a->ne[3]);
-        s->op_params[0] = GGML_SORT_ORDER_DESC;
-        op(s, GGML_OP_ARGSORT, a);
-        ggml_tensor *t = view_of(s, GGML_OP_VIEW, 0);
-        set_shape(t, GGML_TYPE_I32, k, s->ne[1], s->ne[2], s->ne[3]);
-        t->nb[1] = s->nb[1]; t->nb[2] = s->nb[2]; t->nb[3] = s->nb[3];
-        return t;
-    }
-    // an exchange between the ranks of a tensor-parallel model (b200_comm.h): all-reduce in place, or all-gather along ne0
-    ggml_tensor *collective(ggml_tensor *a, int kind, int world) {
-        ggml_tensor *t;
-        if (kind == B200_COLLECTIVE_ALL_REDUCE_SUM) {
-            t = view_of(a, GGML_OP_MAP_CUSTOM1, 0);
-            set_shape(t, a->type, a->ne[0], a->ne[1], a->ne[2], a->ne[3]);
-        } else {
-            t = alloc_result(GGML_TYPE_F32, a->ne[0] * world, a->ne[1], a->ne[2], a->ne[3]);
-            op(t, GGML_OP_MAP_CUSTOM1, a);
-        }
-        t->op_params[0] = (int32_t)B200_COLLECTIVE_TAG;
-        t->op_params[1] = kind;
-        return t;
-    }
-    ggml_tensor *sum_rows(ggml_tensor *a) { return op(alloc_result(GGML_TYPE_F32, 1, a->ne[1], a->ne[2], a->ne[3]), GGML_OP_SUM_ROWS, a); }
-};
-
-}  // namespace
-
-// ------------------------------------------------------------------------------------------------ model
-struct LayerW {
-    ggml_tensor *attn_norm = nullptr, *wq = nullptr, *wk = nullptr, *wv = nullptr, *wo = nullptr, *ffn_norm = nullptr;
-    ggml_tensor *ffn_gate = nullptr, *ffn_up = nullptr, *ffn_down = nullptr;
-    ggml_tensor *ffn_gate_inp = nullptr, *ffn_gate_exps = nullptr, *ffn_up_exps = nullptr, *ffn_down_exps = nullptr;
-};
-
-struct b200_llama {
-    b200_llama_params hp;
-    ggml_backend_t be = nullptr;
-    ggml_backend_buffer_type_t buft = nullptr, split_buft = nullptr;
-    std::map<std::string, ggml_tensor *> weights;
-    std::deque<ggml_tensor> weight_pool;
-    std::vector<ggml_backend_buffer_t> buffers;  // everything to free
-    int64_t weight_bytes = 0, kv_bytes = 0;
-    // resolved weights
-    ggml_tensor *tok_embd = nullptr, *output_norm = nullptr, *output = nullptr, *rope_freqs = nullptr;
-    std::vector<LayerW> layers;
-    // KV cache (one tensor per layer, [n_embd_gqa * n_ctx], src/llama.cpp:3583-3584)
-    std::vector<ggml_tensor *> k_l, v_l;
-    // compute
-    int32_t max_batch = 0;
-    Bump bump;
-    size_t region_inputs = 0, region_half = 0;  // layout of the compute buffer: [inputs | half A | half B | tail]
-    ggml_tensor inp_tokens, inp_pos, inp_mask, inp_out_ids;
-    // pinned staging of the per-call inputs: [tokens | positions | out ids | mask], reused every call behind `in_ev`
-    unsigned char *pin = nullptr;
-    size_t pin_bytes = 0;
-    cudaEvent_t in_ev = nullptr;   // recorded behind the input copies of the last call
-    bool in_ev_pending = false;
-    // what the device-side KQ mask currently holds (single-token decode only moves one element per call)
-    // the graph of the previous call, reusable when only the KV write position moved (single-token decode): per layer the two
-    // destination views of the cache stores and the CPY nodes that alias them
-    struct KvStore { ggml_tensor *view, *cpy; char *base; size_t row; };
-    std::vector<KvStore> kv_stores;
-    int32_t g_n_tokens = 0, g_n_outputs = 0;
-    int64_t g_n_kv = -1;
-    double t_build = 0, t_inputs = 0, t_compute = 0, t_sync = 0;  // host seconds per phase (B200_LLAMA_TIMING=1 prints them at free)
-    int64_t t_calls = 0;
-    int64_t mk_n_kv = -1, mk_rows = -1;
-    int32_t mk_n_tokens = 0, mk_n_past = -1;
-    Arena arena;
-    ggml_cgraph graph;
-    std::vector<ggml_tensor *> graph_nodes;
-    ggml_tensor *logits_t = nullptr;
-    int64_t last_launches = 0;
-    bool finalized = false;
-};
-
-namespace {
-
-#define LL_REQUIRE(cond, code, ...)      \
-    do {                                 \
-        if (!(cond)) {                   \
-            b200::set_error(__VA_ARGS__); \
-            return code;                 \
-        }                                \
-    } while (0)
-
-bool is_matrix_weight(const std::string &name) {
-    // what llama.cpp places in the split buffer type: the 2-D weight matrices of the layers and the output head
-    // (llm_load_tensors uses buft_matrix for them, src/llama.cpp:7039-7062); norms, router and token_embd are not split
-    if (name == "output.weight") return true;
-    if (name.compare(0, 4, "blk.") != 0) return false;
-    static const char *const k[] = {"attn_q.weight", "attn_k.weight", "attn_v.weight", "attn_output.weight", "ffn_gate.weight", "ffn_up.weight", "ffn_down.weight"};
-    for (const char *s : k) {
-        const size_t n = strlen(s);
-        if (name.size() > n && name.compare(name.size() - n, n, s) == 0) return true;
-    }
-    return false;
-}
-
-ggml_tensor *alloc_in_buft(b200_llama *m, ggml_backend_buffer_type_t buft, ggml_tensor *t, int usage) {
-    const size_t sz = buft->iface.get_alloc_size ? buft->iface.get_alloc_size(buft, t) : nbytes(t);
-    ggml_backend_buffer_t buf = buft->iface.alloc_buffer(buft, sz);
-    if (!buf) return nullptr;
-    buf->usage = (ggml_backend_buffer_usage)usage;
-    m->buffers.push_back(buf);
-    t->buffer = buf;
-    t->data = buf->iface.get_base(buf);
-    if (buf->iface.init_tensor) buf->iface.init_tensor(buf, t);
-    return t;
-}
-
-ggml_tensor *find_w(b200_llama *m, const std::string &name) {
-    auto it = m->weights.find(name);
-    return it == m->weights.end() ? nullptr : it->second;
-}
-
-}  // namespace
+const Arch *b200::host::find_arch(int32_t id) { return id == B200_ARCH_GENESUN ? genesun_arch() : nullptr; }
 
 extern "C" int b200_llama_new(const b200_llama_params *p, b200_llama **out) {
     LL_REQUIRE(p && out, B200_ERR_INVALID, "b200_llama_new: NULL argument");
-    LL_REQUIRE(p->n_embd > 0 && p->n_layer > 0 && p->n_head > 0 && p->n_head_kv > 0 && p->n_head % p->n_head_kv == 0 && p->n_vocab > 0 && p->n_ctx > 0,
+    const Arch *arch = find_arch(p->arch);
+    LL_REQUIRE(p->arch == B200_ARCH_LLAMA || arch, B200_ERR_UNSUPPORTED, "b200_llama_new: unknown architecture %d", p->arch);
+    LL_REQUIRE(p->n_embd > 0 && p->n_layer > 0 && p->n_vocab > 0 && p->n_ctx > 0 && (arch || (p->n_head > 0 && p->n_head_kv > 0 && p->n_head % p->n_head_kv == 0)),
                B200_ERR_INVALID, "b200_llama_new: bad hyper-parameters");
     LL_REQUIRE(p->n_ctx % KV_PAD == 0, B200_ERR_INVALID, "b200_llama_new: n_ctx must be a multiple of %d (flash-attention KV padding)", KV_PAD);
-    LL_REQUIRE((p->type_k == B200_TYPE_F16 || p->type_k == B200_TYPE_Q8_0 || p->type_k == B200_TYPE_Q4_0) && p->type_v == p->type_k, B200_ERR_UNSUPPORTED,
+    LL_REQUIRE(arch || ((p->type_k == B200_TYPE_F16 || p->type_k == B200_TYPE_Q8_0 || p->type_k == B200_TYPE_Q4_0) && p->type_v == p->type_k), B200_ERR_UNSUPPORTED,
                "b200_llama_new: KV cache types must be f16/f16, q8_0/q8_0 or q4_0/q4_0");
     LL_REQUIRE(ggml_backend_b200_get_device_count() > 0, B200_ERR_CUDA, "b200_llama_new: no CUDA device (there is no CPU fallback)");
+    LL_REQUIRE(!arch || (p->tp_world <= 1 && p->n_split_devices <= 1), B200_ERR_UNSUPPORTED, "b200_llama_new: %s runs on one device", arch ? arch->name : "");
     if (p->tp_world > 1) {
         LL_REQUIRE(p->tp_rank >= 0 && p->tp_rank < p->tp_world && b200_comm_world() == p->tp_world && b200_comm_rank() == p->tp_rank, B200_ERR_INVALID,
                    "b200_llama_new: tensor-parallel mode needs a communicator of %d ranks (b200_comm_init)", p->tp_world);
@@ -327,8 +28,11 @@ extern "C" int b200_llama_new(const b200_llama_params *p, b200_llama **out) {
     }
     b200_llama *m = new b200_llama();
     m->hp = *p;
+    m->arch = arch;
+    if (m->hp.n_seq_max < 1) m->hp.n_seq_max = 1;
+    if (arch) m->layer_hp.assign((size_t)p->n_layer, b200_layer_params());
     if (m->hp.tp_world < 1) { m->hp.tp_world = 1; m->hp.tp_rank = 0; }
-    if (m->hp.n_embd_head == 0) m->hp.n_embd_head = p->n_embd / p->n_head;
+    if (m->hp.n_embd_head == 0 && p->n_head > 0) m->hp.n_embd_head = p->n_embd / p->n_head;
     if (m->hp.n_ctx_orig == 0) m->hp.n_ctx_orig = p->n_ctx;
     if (m->hp.rope_freq_base == 0.0f) m->hp.rope_freq_base = 10000.0f;
     if (m->hp.rope_freq_scale == 0.0f) m->hp.rope_freq_scale = 1.0f;
@@ -356,6 +60,7 @@ extern "C" int b200_llama_new(const b200_llama_params *p, b200_llama **out) {
 extern "C" void b200_llama_free(b200_llama *m) {
     if (!m) return;
     if (m->be) m->be->iface.synchronize(m->be);
+    if (m->arch && m->arch->release) m->arch->release(m);
     for (ggml_backend_buffer_t b : m->buffers) {
         if (b->iface.free_buffer) b->iface.free_buffer(b);
         delete b;  // ggml_backend_buffer_free: iface.free_buffer(buffer); delete buffer  (ggml-backend.cpp:95-104)
@@ -374,6 +79,30 @@ extern "C" void b200_llama_free(b200_llama *m) {
 extern "C" int b200_llama_set_tensor(b200_llama *m, const char *name, int type, int64_t ne0, int64_t ne1, int64_t ne2, const void *data) {
     LL_REQUIRE(m && name && data, B200_ERR_INVALID, "b200_llama_set_tensor: NULL argument");
     LL_REQUIRE(!m->finalized, B200_ERR_INVALID, "b200_llama_set_tensor: model already finalized");
+    if (m->arch && m->arch->place_tensor) return m->arch->place_tensor(m, name, type, ne0, ne1, ne2, data);
+    return upload_tensor(m, name, type, ne0, ne1, ne2, data);
+}
+
+extern "C" int b200_llama_set_layer(b200_llama *m, int32_t il, const b200_layer_params *lp) {
+    LL_REQUIRE(m && lp, B200_ERR_INVALID, "b200_llama_set_layer: NULL argument");
+    LL_REQUIRE(m->arch, B200_ERR_UNSUPPORTED, "b200_llama_set_layer: the llama architecture has one shape for all layers (b200_llama_params)");
+    LL_REQUIRE(il >= 0 && il < m->hp.n_layer && m->weights.empty() && !m->finalized, B200_ERR_INVALID, "b200_llama_set_layer: layer %d of %d, before any tensor", il, m->hp.n_layer);
+    m->layer_hp[(size_t)il] = *lp;
+    return B200_OK;
+}
+
+ggml_tensor *b200::host::new_device_tensor(b200_llama *m, const char *name, int type, int64_t ne0, int64_t ne1, bool clear) {
+    m->weight_pool.emplace_back();
+    ggml_tensor *t = &m->weight_pool.back();
+    memset(t, 0, sizeof(*t));
+    set_shape(t, type, ne0, ne1, 1, 1);
+    snprintf(t->name, sizeof(t->name), "%s", name);
+    if (!alloc_in_buft(m, m->buft, t, GGML_BACKEND_BUFFER_USAGE_ANY)) { m->weight_pool.pop_back(); return nullptr; }
+    if (clear) t->buffer->iface.clear(t->buffer, 0);
+    return t;
+}
+
+int b200::host::upload_tensor(b200_llama *m, const char *name, int type, int64_t ne0, int64_t ne1, int64_t ne2, const void *data) {
     const TypeTraits tt = type_traits(type);
     LL_REQUIRE(tt.blck > 0 && ne0 > 0 && ne1 > 0 && ne2 > 0 && ne0 % tt.blck == 0, B200_ERR_INVALID, "b200_llama_set_tensor: bad type/shape for %s", name);
     LL_REQUIRE(m->weights.find(name) == m->weights.end(), B200_ERR_INVALID, "b200_llama_set_tensor: duplicate tensor %s", name);
@@ -421,10 +150,170 @@ extern "C" int b200_llama_clone_tensor(b200_llama *m, const char *name, const ch
     return B200_OK;
 }
 
+
+// ------------------------------------------------------------------------------------------------ architectures with their own graph
+namespace {
+
+int round_up(int64_t v, int64_t to) { return (int)((v + to - 1) / to * to); }
+
+// the inputs of a batch step at fixed addresses at the front of the compute buffer
+void make_batch_inputs(b200_llama *m, Bump &bp) {
+    const b200_llama_params &hp = m->hp;
+    auto mk = [&](ggml_tensor *t, int64_t ne0, int64_t ne1, const char *name) {
+        memset(t, 0, sizeof(*t));
+        set_shape(t, GGML_TYPE_I32, ne0, ne1, 1, 1);
+        t->buffer = bp.buf;
+        t->data = bp.take(nbytes(t));
+        t->flags = GGML_TENSOR_FLAG_INPUT;
+        snprintf(t->name, sizeof(t->name), "%s", name);
+    };
+    mk(&m->inp_tokens, m->max_batch, 1, "inp_tokens");
+    mk(&m->inp_pos, m->max_batch, 1, "inp_pos");
+    mk(&m->inp_cells, m->max_batch, 1, "inp_cells");
+    mk(&m->inp_tok_seq, m->max_batch, 1, "inp_tok_seq");
+    mk(&m->inp_out_ids, m->max_batch, 1, "inp_out_ids");
+    mk(&m->inp_cell_seq, hp.n_ctx, 1, "inp_cell_seq");
+    mk(&m->inp_cell_pos, hp.n_ctx, 1, "inp_cell_pos");
+    mk(&m->inp_seq_info, hp.n_seq_max, 4, "inp_seq_info");
+}
+
+int finalize_arch(b200_llama *m, int32_t max_batch) {
+    const b200_llama_params &hp = m->hp;
+    LL_REQUIRE(hp.n_ctx % KV_PAD == 0, B200_ERR_INVALID, "b200_llama_finalize: n_ctx must be a multiple of %d", KV_PAD);
+    int rc = m->arch->finalize(m);
+    if (rc != B200_OK) return rc;
+    m->max_batch = max_batch;
+    m->cache.init(hp.n_ctx, hp.n_seq_max);
+    // size the regions: build the largest graph over fake addresses and read how far each bump allocator went
+    Bump fake;
+    fake.base = (char *)4096; fake.size = (size_t)1 << 60; fake.align = m->buft->iface.get_alignment(m->buft);
+    Bump in = fake;
+    make_batch_inputs(m, in);
+    for (Bump &r : m->regions) r = fake;
+    m->measuring = true;
+    const BatchShape big = {max_batch, hp.n_ctx, max_batch, hp.n_seq_max < max_batch ? hp.n_seq_max : max_batch};
+    rc = m->arch->build(m, big);
+    m->measuring = false;
+    if (rc != B200_OK) return rc;
+    size_t need[b200_llama::N_REGIONS], total = in.off + 4096;
+    for (int i = 0; i < b200_llama::N_REGIONS; i++) { need[i] = (m->regions[i].peak + 4095) / 4096 * 4096 + 4096; total += need[i]; }
+    ggml_backend_buffer_t cb = m->buft->iface.alloc_buffer(m->buft, total);
+    LL_REQUIRE(cb, B200_ERR_NOMEM, "b200_llama_finalize: out of device memory for the compute buffer (%zu bytes)", total);
+    cb->usage = GGML_BACKEND_BUFFER_USAGE_COMPUTE;
+    m->buffers.push_back(cb);
+    char *base = (char *)cb->iface.get_base(cb);
+    m->bump.buf = cb; m->bump.base = base; m->bump.size = in.off + 4096; m->bump.align = fake.align; m->bump.off = 0;
+    make_batch_inputs(m, m->bump);
+    size_t off = (in.off + 4095) / 4096 * 4096;
+    for (int i = 0; i < b200_llama::N_REGIONS; i++) {
+        Bump &r = m->regions[i];
+        r.buf = cb; r.base = base + off; r.size = need[i]; r.off = 0; r.align = fake.align;
+        off += need[i];
+    }
+    m->graph.n_nodes = 0;
+    m->g_shape = {0, 0, 0, 0};
+    const size_t pin_need = 4 * ((size_t)5 * max_batch + 2 * (size_t)hp.n_ctx + 4 * (size_t)hp.n_seq_max) + 256;
+    LL_REQUIRE(cudaHostAlloc((void **)&m->pin, pin_need, cudaHostAllocDefault) == cudaSuccess, B200_ERR_NOMEM, "b200_llama_finalize: cannot pin %zu bytes of input staging", pin_need);
+    m->pin_bytes = pin_need;
+    m->finalized = true;
+    return B200_OK;
+}
+
+}  // namespace
+
+extern "C" int b200_llama_seq_open(b200_llama *m, int32_t *seq_id) {
+    LL_REQUIRE(m && seq_id && m->finalized && m->arch, B200_ERR_INVALID, "b200_llama_seq_open: needs a finalized model of an architecture with sequences");
+    const int32_t id = m->cache.open_seq();
+    LL_REQUIRE(id >= 0, B200_ERR_NOMEM, "b200_llama_seq_open: all %d sequences are open", m->hp.n_seq_max);
+    *seq_id = id;
+    return B200_OK;
+}
+extern "C" int b200_llama_seq_close(b200_llama *m, int32_t seq_id) {
+    LL_REQUIRE(m && m->finalized && m->arch && m->cache.is_open(seq_id), B200_ERR_INVALID, "b200_llama_seq_close: sequence %d is not open", seq_id);
+    m->cache.close_seq(seq_id);
+    return B200_OK;
+}
+extern "C" int b200_llama_seq_length(b200_llama *m, int32_t seq_id) {
+    return m && m->arch && m->cache.is_open(seq_id) ? m->cache.seqs[(size_t)seq_id].len : -1;
+}
+
+extern "C" int b200_llama_decode_batch(b200_llama *m, const int32_t *tokens, const int32_t *seq_ids, const int8_t *want, int32_t n_tokens, float *logits) {
+    LL_REQUIRE(m && m->finalized && m->arch && tokens && seq_ids, B200_ERR_INVALID, "b200_llama_decode_batch: needs a finalized model of an architecture with sequences");
+    LL_REQUIRE(n_tokens > 0 && n_tokens <= m->max_batch, B200_ERR_INVALID, "b200_llama_decode_batch: n_tokens %d outside (0, %d]", n_tokens, m->max_batch);
+    const b200_llama_params &hp = m->hp;
+    SeqCache &kc = m->cache;
+    // the runs of the batch: one per sequence, adjacent tokens
+    std::vector<int32_t> &info = m->st_info;
+    std::vector<int32_t> run_first, run_count, run_seq;
+    for (int i = 0; i < n_tokens; i++) {
+        LL_REQUIRE(tokens[i] >= 0 && tokens[i] < hp.n_vocab, B200_ERR_INVALID, "b200_llama_decode_batch: token id out of range");
+        LL_REQUIRE(kc.is_open(seq_ids[i]), B200_ERR_INVALID, "b200_llama_decode_batch: sequence %d is not open", seq_ids[i]);
+        if (i == 0 || seq_ids[i] != seq_ids[i - 1]) {
+            for (int32_t s : run_seq) LL_REQUIRE(s != seq_ids[i], B200_ERR_INVALID, "b200_llama_decode_batch: the tokens of sequence %d are not adjacent", seq_ids[i]);
+            run_first.push_back(i); run_count.push_back(0); run_seq.push_back(seq_ids[i]);
+        }
+        run_count.back()++;
+    }
+    LL_REQUIRE(n_tokens <= kc.n_cells() - kc.n_used, B200_ERR_NOMEM, "b200_llama_decode_batch: the cache is full (%d cells, %d in use, %d asked for)", kc.n_cells(), kc.n_used, n_tokens);
+    const int32_t n_seq = (int32_t)run_seq.size();
+    m->st_cells.resize((size_t)n_tokens); m->st_pos.resize((size_t)n_tokens); m->st_seq.assign(seq_ids, seq_ids + n_tokens);
+    info.assign((size_t)4 * n_seq, 0);
+    for (int32_t r = 0; r < n_seq; r++) {
+        info[(size_t)r] = run_first[(size_t)r]; info[(size_t)n_seq + r] = run_count[(size_t)r]; info[(size_t)2 * n_seq + r] = run_seq[(size_t)r];
+        info[(size_t)3 * n_seq + r] = kc.seqs[(size_t)run_seq[(size_t)r]].fresh ? 1 : 0;
+        kc.place(run_seq[(size_t)r], run_count[(size_t)r], m->st_cells.data() + run_first[(size_t)r], m->st_pos.data() + run_first[(size_t)r]);
+        kc.seqs[(size_t)run_seq[(size_t)r]].fresh = false;
+    }
+    m->st_out.clear();
+    for (int i = 0; i < n_tokens; i++) if (want && want[i]) m->st_out.push_back(i);
+    const int32_t n_out = (int32_t)m->st_out.size();
+    LL_REQUIRE(n_out == 0 || logits, B200_ERR_INVALID, "b200_llama_decode_batch: logits wanted but no buffer given");
+    int32_t n_kv = round_up(kc.high, KV_PAD);
+    if (n_kv > hp.n_ctx) n_kv = hp.n_ctx;
+    const BatchShape bs = {n_tokens, n_kv, n_out, n_seq};
+    if (m->graph.n_nodes == 0 || memcmp(&bs, &m->g_shape, sizeof(bs)) != 0) {
+        m->graph.n_nodes = 0;
+        const int rc = m->arch->build(m, bs);
+        if (rc != B200_OK) return rc;
+        m->g_shape = bs;
+    }
+    ggml_backend_t be = m->be;
+    if (m->in_ev_pending) { cudaEventSynchronize(m->in_ev); m->in_ev_pending = false; }
+    int32_t *pin = (int32_t *)m->pin;
+    auto send = [&](ggml_tensor *t, const int32_t *src, size_t n) {
+        if (n == 0) return;
+        memcpy(pin, src, 4 * n);
+        be->iface.set_tensor_async(be, t, pin, 0, 4 * n);
+        pin += n;
+    };
+    send(&m->inp_tokens, tokens, (size_t)n_tokens);
+    send(&m->inp_pos, m->st_pos.data(), (size_t)n_tokens);
+    send(&m->inp_cells, m->st_cells.data(), (size_t)n_tokens);
+    send(&m->inp_tok_seq, m->st_seq.data(), (size_t)n_tokens);
+    send(&m->inp_out_ids, m->st_out.data(), (size_t)n_out);
+    send(&m->inp_cell_seq, kc.cell_seq.data(), (size_t)n_kv);
+    send(&m->inp_cell_pos, kc.cell_pos.data(), (size_t)n_kv);
+    send(&m->inp_seq_info, info.data(), (size_t)4 * n_seq);
+    if (!m->in_ev) LL_REQUIRE(cudaEventCreateWithFlags(&m->in_ev, cudaEventDisableTiming) == cudaSuccess, B200_ERR_CUDA, "b200_llama_decode_batch: cudaEventCreate failed");
+    if (cudaEventRecord(m->in_ev, (cudaStream_t)ggml_backend_b200_get_stream(be)) == cudaSuccess) m->in_ev_pending = true;
+    else { cudaGetLastError(); cudaStreamSynchronize((cudaStream_t)ggml_backend_b200_get_stream(be)); }
+    int64_t l0 = 0, l1 = 0;
+    ggml_backend_b200_get_stats(&l0, nullptr, nullptr);
+    const ggml_status st = be->iface.graph_compute(be, &m->graph);
+    ggml_backend_b200_get_stats(&l1, nullptr, nullptr);
+    m->last_launches = l1 - l0;
+    m->t_calls++;
+    LL_REQUIRE(st == GGML_STATUS_SUCCESS, B200_ERR_CUDA, "b200_llama_decode_batch: graph_compute failed (%d)", (int)st);
+    if (n_out > 0) be->iface.get_tensor_async(be, m->logits_t, logits, 0, 4 * (size_t)hp.n_vocab * (size_t)n_out);
+    be->iface.synchronize(be);
+    return B200_OK;
+}
+
 // ------------------------------------------------------------------------------------------------ finalize
 extern "C" int b200_llama_finalize(b200_llama *m, int32_t max_batch) {
     LL_REQUIRE(m && max_batch > 0, B200_ERR_INVALID, "b200_llama_finalize: bad argument");
     LL_REQUIRE(!m->finalized, B200_ERR_INVALID, "b200_llama_finalize: called twice");
+    if (m->arch) return finalize_arch(m, max_batch);
     const b200_llama_params &hp = m->hp;
     const bool moe = hp.n_expert > 0;
     m->tok_embd = find_w(m, "token_embd.weight");
@@ -504,7 +393,7 @@ extern "C" int b200_llama_finalize(b200_llama *m, int32_t max_batch) {
 }
 
 extern "C" int b200_llama_kv_write(b200_llama *m, int32_t il, int32_t is_v, int32_t cell0, int32_t n, const void *data) {
-    LL_REQUIRE(m && m->finalized && data, B200_ERR_INVALID, "b200_llama_kv_write: bad argument");
+    LL_REQUIRE(m && m->finalized && data && !m->arch, B200_ERR_INVALID, "b200_llama_kv_write: bad argument");
     LL_REQUIRE(il >= 0 && il < m->hp.n_layer && cell0 >= 0 && n >= 0 && cell0 + n <= m->hp.n_ctx, B200_ERR_INVALID, "b200_llama_kv_write: range");
     ggml_tensor *t = (is_v ? m->v_l : m->k_l)[(size_t)il];
     const size_t row = row_size(t->type, (int64_t)m->hp.n_embd_head * (m->hp.n_head_kv / m->hp.tp_world));
@@ -513,7 +402,7 @@ extern "C" int b200_llama_kv_write(b200_llama *m, int32_t il, int32_t is_v, int3
 }
 
 extern "C" int b200_llama_kv_read(b200_llama *m, int32_t il, int32_t is_v, int32_t cell0, int32_t n, void *data) {
-    LL_REQUIRE(m && m->finalized && data, B200_ERR_INVALID, "b200_llama_kv_read: bad argument");
+    LL_REQUIRE(m && m->finalized && data && !m->arch, B200_ERR_INVALID, "b200_llama_kv_read: bad argument");
     LL_REQUIRE(il >= 0 && il < m->hp.n_layer && cell0 >= 0 && n >= 0 && cell0 + n <= m->hp.n_ctx, B200_ERR_INVALID, "b200_llama_kv_read: range");
     ggml_tensor *t = (is_v ? m->v_l : m->k_l)[(size_t)il];
     const size_t row = row_size(t->type, (int64_t)m->hp.n_embd_head * (m->hp.n_head_kv / m->hp.tp_world));
@@ -682,6 +571,7 @@ int build_graph(b200_llama *m, int32_t n_tokens, int32_t n_past, int32_t n_outpu
 
 int enqueue_decode(b200_llama *m, const int32_t *tokens, int32_t n_tokens, int32_t n_past, float *logits, int32_t logits_all) {
     LL_REQUIRE(m && m->finalized && tokens, B200_ERR_INVALID, "b200_llama_decode: bad argument");
+    LL_REQUIRE(!m->arch, B200_ERR_UNSUPPORTED, "b200_llama_decode: this architecture steps through b200_llama_decode_batch");
     LL_REQUIRE(n_tokens > 0 && n_tokens <= m->max_batch, B200_ERR_INVALID, "b200_llama_decode: n_tokens %d outside (0, %d]", n_tokens, m->max_batch);
     LL_REQUIRE(n_past >= 0 && n_past + n_tokens <= m->hp.n_ctx, B200_ERR_INVALID, "b200_llama_decode: context overflow");
     for (int i = 0; i < n_tokens; i++) LL_REQUIRE(tokens[i] >= 0 && tokens[i] < m->hp.n_vocab, B200_ERR_INVALID, "b200_llama_decode: token id out of range");

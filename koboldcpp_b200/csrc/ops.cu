@@ -2,6 +2,8 @@
 // the device with no CPU fallback.  All of them are HBM/L2-bound elementwise or row-reduction kernels; the design rule
 // is vector access + one pass.  Semantics cite /root/reference/ggml/src/ggml.c; see include/b200_ggml_ops.h.
 #include "b200_common.cuh"
+
+#include <cuda_bf16.h>
 #include "rope_kv.cuh"
 #include "../../include/b200_ggml_ops.h"
 
@@ -249,6 +251,7 @@ template <> __device__ __forceinline__ __half cvt<float, __half>(float v) { retu
 template <> __device__ __forceinline__ float  cvt<__half, float>(__half v) { return __half2float(v); }
 template <> __device__ __forceinline__ __half cvt<__half, __half>(__half v) { return v; }
 template <> __device__ __forceinline__ int    cvt<int, int>(int v) { return v; }
+template <> __device__ __forceinline__ float  cvt<__nv_bfloat16, float>(__nv_bfloat16 v) { return __bfloat162float(v); }
 
 // `ind` (optional): device slot holding the destination base pointer, read at run time -- lets a captured CUDA graph
 // follow a KV-cache write position that moves every token without being re-captured or patched.
@@ -911,8 +914,8 @@ extern "C" int b200_op_sum_rows(const b200_tensor *x, const b200_tensor *dst, b2
 
 extern "C" int b200_op_mul_mat_float(const b200_tensor *w, const b200_tensor *x, const b200_tensor *dst, b200_stream_t stream) {
     REQUIRE(w && x && dst && w->data && x->data && dst->data, B200_ERR_INVALID, "b200_op_mul_mat_float: NULL argument");
-    REQUIRE((w->type == B200_TYPE_F32 || w->type == B200_TYPE_F16) && x->type == B200_TYPE_F32 && dst->type == B200_TYPE_F32, B200_ERR_UNSUPPORTED,
-            "b200_op_mul_mat_float: f32/f16 weights, f32 activations");
+    REQUIRE((w->type == B200_TYPE_F32 || w->type == B200_TYPE_F16 || w->type == B200_TYPE_BF16) && x->type == B200_TYPE_F32 && dst->type == B200_TYPE_F32, B200_ERR_UNSUPPORTED,
+            "b200_op_mul_mat_float: f32/f16/bf16 weights, f32 activations");
     REQUIRE(w->nb[0] == (size_t)type_block_bytes(w->type) && x->nb[0] == 4, B200_ERR_UNSUPPORTED, "b200_op_mul_mat_float: rows must be contiguous");
     REQUIRE(w->ne[0] == x->ne[0] && dst->ne[0] == w->ne[1] && dst->ne[1] == x->ne[1] && dst->ne[2] == x->ne[2] && dst->ne[3] == x->ne[3] &&
             w->ne[2] > 0 && w->ne[3] > 0 && x->ne[2] % w->ne[2] == 0 && x->ne[3] % w->ne[3] == 0, B200_ERR_INVALID, "b200_op_mul_mat_float: shape mismatch");
@@ -920,6 +923,7 @@ extern "C" int b200_op_mul_mat_float(const b200_tensor *w, const b200_tensor *x,
     if (total == 0) return B200_OK;
     const unsigned g = grid1d(total * 32, 256);
     if (w->type == B200_TYPE_F32) mul_mat_float_kernel<float><<<g, 256, 0, (cudaStream_t)stream>>>(td(w), td(x), td(dst));
+    else if (w->type == B200_TYPE_BF16) mul_mat_float_kernel<__nv_bfloat16><<<g, 256, 0, (cudaStream_t)stream>>>(td(w), td(x), td(dst));
     else mul_mat_float_kernel<__half><<<g, 256, 0, (cudaStream_t)stream>>>(td(w), td(x), td(dst));
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
