@@ -64,6 +64,23 @@ class FattnArgs(C.Structure):
                 ("scale", C.c_float), ("max_bias", C.c_float), ("logit_softcap", C.c_float)]
 
 
+class LatentAttnArgs(C.Structure):
+    """b200_latent_attn_args (include/b200_ggml_ops.h); strides in floats."""
+    _fields_ = [("q_lat", C.c_void_p), ("q_lat_s_head", C.c_int64), ("q_lat_s_tok", C.c_int64), ("q_rot", C.c_void_p), ("q_rot_s_head", C.c_int64),
+                ("q_rot_s_tok", C.c_int64), ("cache", C.c_void_p), ("cache_stride", C.c_int64), ("cell_seq", C.c_void_p), ("cell_pos", C.c_void_p),
+                ("tok_seq", C.c_void_p), ("tok_pos", C.c_void_p), ("sink", C.c_void_p), ("dst", C.c_void_p), ("dst_s_head", C.c_int64), ("dst_s_tok", C.c_int64),
+                ("kv_rank", C.c_int32), ("rot_dim", C.c_int32), ("n_head", C.c_int32), ("n_tokens", C.c_int32), ("n_kv", C.c_int32), ("window", C.c_int32),
+                ("scale", C.c_float)]
+
+
+class MlstmArgs(C.Structure):
+    """b200_mlstm_args (include/b200_ggml_ops.h); strides in floats."""
+    _fields_ = [("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("ig", C.c_void_p), ("fg", C.c_void_p), ("q_stride", C.c_int64), ("k_stride", C.c_int64),
+                ("v_stride", C.c_int64), ("g_stride", C.c_int64), ("i_bias", C.c_void_p), ("f_bias", C.c_void_p), ("seq_info", C.c_void_p), ("n_seq", C.c_int32),
+                ("state", C.c_void_p), ("slot_stride", C.c_int64), ("dst", C.c_void_p), ("dst_stride", C.c_int64), ("heads", C.c_int32), ("dim", C.c_int32),
+                ("vdim", C.c_int32), ("gate_cap", C.c_float), ("q_scale", C.c_float)]
+
+
 _SIGS = {
     # name: (restype, argtypes)
     "b200_last_error": (C.c_char_p, []),
@@ -119,6 +136,17 @@ _OPS_SIGS = {
     "b200_op_moe_router": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
                                       C.c_int64, C.c_void_p]),
     "b200_op_silu_mul": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
+    "b200_op_norm": (C.c_int, [C.POINTER(Tensor), C.c_void_p, C.c_int64, C.POINTER(Tensor), C.c_void_p, C.POINTER(Tensor), C.POINTER(Tensor), C.c_float, C.c_int, C.c_void_p]),
+    "b200_op_polynorm": (C.c_int, [C.POINTER(Tensor), C.c_void_p, C.POINTER(Tensor), C.c_float, C.c_void_p]),
+    "b200_op_rope_table": (C.c_int, [C.POINTER(Tensor), C.c_void_p, C.c_void_p, C.POINTER(Tensor), C.c_int32, C.c_int32, C.c_float, C.c_void_p]),
+    "b200_op_weighted_sum": (C.c_int, [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
+    "b200_op_sigmoid_mul": (C.c_int, [C.POINTER(Tensor), C.POINTER(Tensor), C.POINTER(Tensor), C.c_void_p]),
+    "b200_op_latent_kv_store": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32,
+                                          C.c_int32, C.c_float, C.c_float, C.c_int32, C.c_void_p]),
+    "b200_op_latent_attn": (C.c_int, [C.POINTER(LatentAttnArgs), C.c_void_p]),
+    "b200_mlstm_state_floats": (C.c_int64, [C.c_int32, C.c_int32, C.c_int32]),
+    "b200_op_mlstm_scan": (C.c_int, [C.POINTER(MlstmArgs), C.c_void_p]),
+    "b200_op_mul_mat_float": (C.c_int, [C.POINTER(Tensor), C.POINTER(Tensor), C.POINTER(Tensor), C.c_void_p]),
     "b200_op_rms_norm_mul": (C.c_int, [C.POINTER(Tensor), C.c_void_p, C.c_void_p, C.POINTER(Tensor), C.c_float, C.c_void_p]),
 }
 
