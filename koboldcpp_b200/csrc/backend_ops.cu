@@ -337,12 +337,29 @@ static void run_mul_mat_split(ExecCtx &x, const ggml_tensor *n) {
     }
 }
 
+static bool bf16_gemm_ok(const ggml_tensor *n);
+
 static void run_mul_mat(ExecCtx &x, const ggml_tensor *n) {
     const ggml_tensor *w = n->src[0], *a = n->src[1];
     const void *xb_prev = x.xb_src;  // only the plain prefill GEMM below keeps the bf16 activations in the scratch meaningful
     x.xb_src = nullptr;
     if (in_split_buffer(w)) { run_mul_mat_split(x, n); return; }
     if (!is_quantized(w->type)) {
+        if (bf16_gemm_ok(n) && node_scratch_bytes(n) <= x.scratch_bytes) {
+            // prompt batches over dense bf16 weights: the tensor-core GEMM, one launch per (i2, i3) slice of a per-head product
+            const int64_t K = w->ne[0], M = w->ne[1], N = a->ne[1];
+            const int64_t r2 = a->ne[2] / w->ne[2], r3 = a->ne[3] / w->ne[3];
+            for (int64_t i13 = 0; i13 < a->ne[3]; i13++) {
+                for (int64_t i12 = 0; i12 < a->ne[2]; i12++) {
+                    const char *ws = (const char *)w->data + (i12 / r2) * w->nb[2] + (i13 / r3) * w->nb[3];
+                    const float *xp = (const float *)((const char *)a->data + i12 * a->nb[2] + i13 * a->nb[3]);
+                    float *dp = (float *)((char *)n->data + i12 * n->nb[2] + i13 * n->nb[3]);
+                    B200_CHECK_RC(b200_mul_mat_q(w->type, ws, w->nb[1], xp, (int64_t)(a->nb[1] / 4), dp, (int64_t)(n->nb[1] / 4), K, M, N, x.scratch, x.scratch_bytes, x.stream));
+                    x.launches += 2;
+                }
+            }
+            return;
+        }
         b200_tensor tw = as_b200(w), ta = as_b200(a), td = as_b200(n);
         B200_CHECK_RC(b200_op_mul_mat_float(&tw, &ta, &td, x.stream));
         x.launches++;
@@ -436,7 +453,17 @@ size_t node_fa_workspace(const ggml_tensor *n) {
     return b200_flash_attn_workspace_bytes(&a);
 }
 
+// a MUL_MAT over dense bf16 weights with enough columns for the tensor cores, in the layout the GEMM takes
+static bool bf16_gemm_ok(const ggml_tensor *n) {
+    const ggml_tensor *w = n->src[0], *a = n->src[1];
+    if (n->op != GGML_OP_MUL_MAT || !w || !a || w->type != GGML_TYPE_BF16 || a->type != GGML_TYPE_F32 || a->ne[1] <= 8) return false;
+    if (w->ne[0] % 64 || ((uintptr_t)w->data | w->nb[1] | w->nb[2] | w->nb[3]) & 15) return false;
+    if (((uintptr_t)a->data | a->nb[1] | a->nb[2] | a->nb[3]) & 15 || a->nb[0] != 4 || n->nb[0] != 4 || (n->nb[1] & 3)) return false;
+    return w->ne[2] > 0 && w->ne[3] > 0 && a->ne[2] % w->ne[2] == 0 && a->ne[3] % w->ne[3] == 0 && a->ne[2] * a->ne[3] <= 4096;
+}
+
 size_t node_scratch_bytes(const ggml_tensor *n) {
+    if (bf16_gemm_ok(n)) return b200_mul_mat_q_workspace_bytes(n->src[0]->type, n->src[0]->ne[0], n->src[0]->ne[1], n->src[1]->ne[1]);
     if (n->op == GGML_OP_MUL_MAT_ID && n->src[0] && n->src[2] && n->src[2]->ne[0] * n->src[2]->ne[1] > B200_GEMV_MAX_JOBS)
         return b200_mul_mat_id_q_workspace_bytes(n->src[0]->type, n->src[0]->ne[0], n->src[0]->ne[1], n->src[2]->ne[0], n->src[2]->ne[1], (int32_t)n->src[0]->ne[2]);
     if (n->op != GGML_OP_MUL_MAT || !n->src[0] || !n->src[1] || !is_quantized(n->src[0]->type) || n->src[1]->ne[1] <= 8) return 0;

@@ -701,11 +701,13 @@ __global__ void __launch_bounds__(MQ2_THREADS, 1) mmq_tc2_kernel(const __grid_co
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
     const int64_t m0 = (int64_t)blockIdx.x * MQ_BM;
-    const int nsb_all = (int)(p.K / 256);
-    // split-K: this CTA's 256-value groups [sb0, sb0 + nsb)
+    // K steps (64 values) per group: quantised formats are unpacked 256 values at a time, dense bf16 rows step by step
+    constexpr int KPG = TYPE == B200_TYPE_BF16 ? 1 : 4;
+    const int nsb_all = (int)(p.K / (MQ_BK * KPG));
+    // split-K: this CTA's groups [sb0, sb0 + nsb)
     const int ksplit = GROUPED ? 1 : p.ksplit;
     const int sb0 = (int)(((int64_t)blockIdx.z * nsb_all) / ksplit);
-    const int nsb = (int)(((int64_t)(blockIdx.z + 1) * nsb_all) / ksplit) - sb0, nkb = nsb * 4;
+    const int nsb = (int)(((int64_t)(blockIdx.z + 1) * nsb_all) / ksplit) - sb0, nkb = nsb * KPG;
 
     if (tid == 0) {
         for (int s = 0; s < MQ2_STAGES; s++) { mbar_init(&full_bar[s], MQ_PRODUCERS + 1); mbar_init(&empty_bar[s], 1); }
@@ -723,44 +725,6 @@ __global__ void __launch_bounds__(MQ2_THREADS, 1) mmq_tc2_kernel(const __grid_co
         const bool row_ok = m < p.M;
         const unsigned char *wrow = Wbase + (size_t)(row_ok ? m : 0) * p.w_row_bytes;
         const unsigned a_off = (unsigned)((tid >> 3) * 1024 + (tid & 7) * 128);
-        // software pipeline: the raw bytes of group sb+1 are in flight (registers) while group sb is unpacked
-        constexpr int NW = group256_words(TYPE);
-        unsigned cur[NW], nxt[NW];
-        auto fetch = [&](unsigned (&w)[NW], int sb) {
-            if (row_ok) {
-                if constexpr (TYPE == B200_TYPE_Q4_K || TYPE == B200_TYPE_Q5_K) {  // 16-byte aligned rows: LDG.128
-                    const uint4 *q4 = reinterpret_cast<const uint4 *>(wrow + (size_t)sb * G256);
-#pragma unroll
-                    for (int i = 0; i < NW / 4; i++) {
-                        const uint4 v = __ldg(q4 + i);
-                        w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
-                    }
-                } else {
-                    // 2-byte aligned rows: 16-byte loads from the aligned-down address (a quarter of the LSU sector traffic of
-                    // 4-byte loads), then a word select (offset 0..3 words) and a funnel shift (0 or 2 bytes) per word
-                    const uintptr_t a = (uintptr_t)(wrow + (size_t)sb * G256);
-                    const uint4 *q4 = reinterpret_cast<const uint4 *>(a & ~(uintptr_t)15);
-                    const unsigned off = (unsigned)(a & 15) >> 2, sh = (unsigned)(a & 3) * 8;
-                    constexpr int NV = (NW + 1 + 3 + 3) / 4;
-                    unsigned t[NV * 4];
-#pragma unroll
-                    for (int i = 0; i < NV; i++) {
-                        const uint4 v = __ldg(q4 + i);
-                        t[4 * i] = v.x; t[4 * i + 1] = v.y; t[4 * i + 2] = v.z; t[4 * i + 3] = v.w;
-                    }
-                    unsigned prev = (off & 2) ? ((off & 1) ? t[3] : t[2]) : ((off & 1) ? t[1] : t[0]);
-#pragma unroll
-                    for (int i = 0; i < NW; i++) {
-                        const unsigned nx = (off & 2) ? ((off & 1) ? t[i + 4] : t[i + 3]) : ((off & 1) ? t[i + 2] : t[i + 1]);
-                        w[i] = __funnelshift_r(prev, nx, sh);
-                        prev = nx;
-                    }
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < NW; i++) w[i] = 0u;
-            }
-        };
         auto publish = [&](int kb, const unsigned (&o)[32]) {
             const int s = kb % MQ2_STAGES;
             mbar_wait(&empty_bar[s], ((unsigned)(kb / MQ2_STAGES) & 1u) ^ 1u);
@@ -771,17 +735,76 @@ __global__ void __launch_bounds__(MQ2_THREADS, 1) mmq_tc2_kernel(const __grid_co
             fence_proxy_async_smem();
             mbar_arrive(&full_bar[s]);
         };
-        fetch(cur, sb0);
-#pragma unroll 1
-        for (int sb = 0; sb < nsb; sb++) {
-            if (sb + 1 < nsb) fetch(nxt, sb0 + sb + 1);
-            unsigned o[32];
-            DequantR<TYPE, 0>::run(cur, o); publish(sb * 4 + 0, o);
-            DequantR<TYPE, 1>::run(cur, o); publish(sb * 4 + 1, o);
-            DequantR<TYPE, 2>::run(cur, o); publish(sb * 4 + 2, o);
-            DequantR<TYPE, 3>::run(cur, o); publish(sb * 4 + 3, o);
+        if constexpr (TYPE == B200_TYPE_BF16) {
+            // dense bf16 rows: a K step is 128 bytes of the thread's row, stored as it is; the next step's bytes are in flight meanwhile
+            const uint4 *q4 = reinterpret_cast<const uint4 *>(wrow) + (size_t)sb0 * 8;
+            uint4 cur[8], nxt[8];
 #pragma unroll
-            for (int i = 0; i < NW; i++) cur[i] = nxt[i];
+            for (int i = 0; i < 8; i++) cur[i] = row_ok ? __ldg(q4 + i) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll 1
+            for (int kb = 0; kb < nkb; kb++) {
+                if (kb + 1 < nkb) {
+#pragma unroll
+                    for (int i = 0; i < 8; i++) nxt[i] = row_ok ? __ldg(q4 + (size_t)(kb + 1) * 8 + i) : make_uint4(0u, 0u, 0u, 0u);
+                }
+                unsigned o[32];
+#pragma unroll
+                for (int i = 0; i < 8; i++) { o[4 * i] = cur[i].x; o[4 * i + 1] = cur[i].y; o[4 * i + 2] = cur[i].z; o[4 * i + 3] = cur[i].w; }
+                publish(kb, o);
+#pragma unroll
+                for (int i = 0; i < 8; i++) cur[i] = nxt[i];
+            }
+        } else {
+            // software pipeline: the raw bytes of group sb+1 are in flight (registers) while group sb is unpacked
+            constexpr int NW = group256_words(TYPE);
+            unsigned cur[NW], nxt[NW];
+            auto fetch = [&](unsigned (&w)[NW], int sb) {
+                if (row_ok) {
+                    if constexpr (TYPE == B200_TYPE_Q4_K || TYPE == B200_TYPE_Q5_K) {  // 16-byte aligned rows: LDG.128
+                        const uint4 *q4 = reinterpret_cast<const uint4 *>(wrow + (size_t)sb * G256);
+    #pragma unroll
+                        for (int i = 0; i < NW / 4; i++) {
+                            const uint4 v = __ldg(q4 + i);
+                            w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+                        }
+                    } else {
+                        // 2-byte aligned rows: 16-byte loads from the aligned-down address (a quarter of the LSU sector traffic of
+                        // 4-byte loads), then a word select (offset 0..3 words) and a funnel shift (0 or 2 bytes) per word
+                        const uintptr_t a = (uintptr_t)(wrow + (size_t)sb * G256);
+                        const uint4 *q4 = reinterpret_cast<const uint4 *>(a & ~(uintptr_t)15);
+                        const unsigned off = (unsigned)(a & 15) >> 2, sh = (unsigned)(a & 3) * 8;
+                        constexpr int NV = (NW + 1 + 3 + 3) / 4;
+                        unsigned t[NV * 4];
+    #pragma unroll
+                        for (int i = 0; i < NV; i++) {
+                            const uint4 v = __ldg(q4 + i);
+                            t[4 * i] = v.x; t[4 * i + 1] = v.y; t[4 * i + 2] = v.z; t[4 * i + 3] = v.w;
+                        }
+                        unsigned prev = (off & 2) ? ((off & 1) ? t[3] : t[2]) : ((off & 1) ? t[1] : t[0]);
+    #pragma unroll
+                        for (int i = 0; i < NW; i++) {
+                            const unsigned nx = (off & 2) ? ((off & 1) ? t[i + 4] : t[i + 3]) : ((off & 1) ? t[i + 2] : t[i + 1]);
+                            w[i] = __funnelshift_r(prev, nx, sh);
+                            prev = nx;
+                        }
+                    }
+                } else {
+    #pragma unroll
+                    for (int i = 0; i < NW; i++) w[i] = 0u;
+                }
+            };
+            fetch(cur, sb0);
+    #pragma unroll 1
+            for (int sb = 0; sb < nsb; sb++) {
+                if (sb + 1 < nsb) fetch(nxt, sb0 + sb + 1);
+                unsigned o[32];
+                DequantR<TYPE, 0>::run(cur, o); publish(sb * 4 + 0, o);
+                DequantR<TYPE, 1>::run(cur, o); publish(sb * 4 + 1, o);
+                DequantR<TYPE, 2>::run(cur, o); publish(sb * 4 + 2, o);
+                DequantR<TYPE, 3>::run(cur, o); publish(sb * 4 + 3, o);
+    #pragma unroll
+                for (int i = 0; i < NW; i++) cur[i] = nxt[i];
+            }
         }
         mbar_wait(&tmem_full_bar, 0u);
         tc_fence_after();
@@ -830,7 +853,7 @@ __global__ void __launch_bounds__(MQ2_THREADS, 1) mmq_tc2_kernel(const __grid_co
                 const int s = kb % MQ2_STAGES;
                 mbar_wait(&empty_bar[s], ((unsigned)(kb / MQ2_STAGES) & 1u) ^ 1u);
                 mbar_expect_tx(&full_bar[s], (unsigned)B_BYTES);
-                tma_load_2d(smem + (size_t)s * STAGE_BYTES + A_BYTES, &tmB, (sb0 * 4 + kb) * MQ_BK, (int)n0, &full_bar[s]);
+                tma_load_2d(smem + (size_t)s * STAGE_BYTES + A_BYTES, &tmB, (sb0 * KPG + kb) * MQ_BK, (int)n0, &full_bar[s]);
             }
         }
     }
@@ -916,6 +939,15 @@ static int mmq2_launch(const MmqParams &p, int64_t n_pad, cudaStream_t st, unsig
 
 template <int TYPE>
 static int mmq_dispatch_bn(const MmqParams &p, cudaStream_t st) {
+    if constexpr (TYPE == B200_TYPE_BF16) {  // dense rows: the asynchronous kernel only, any K that is a multiple of the K step
+        const int64_t n_pad = mmq_n_pad(p.N);
+        switch (mmq_bn(p.N)) {
+            case 32: return mmq2_launch<TYPE, 32>(p, n_pad, st);
+            case 64: return mmq2_launch<TYPE, 64>(p, n_pad, st);
+            case 128: return mmq2_launch<TYPE, 128>(p, n_pad, st);
+            default: return mmq2_launch<TYPE, 256>(p, n_pad, st);
+        }
+    } else
     if (p.K % 256 == 0 && !getenv("B200_MMQ_V1")) {
         const int64_t n_pad = mmq_n_pad(p.N);
         switch (mmq_bn(p.N)) {
@@ -925,12 +957,15 @@ static int mmq_dispatch_bn(const MmqParams &p, cudaStream_t st) {
             default: return mmq2_launch<TYPE, 256>(p, n_pad, st);
         }
     }
-    switch (mmq_bn(p.N)) {
-        case 32: return mmq_launch<TYPE, 32>(p, st);
-        case 64: return mmq_launch<TYPE, 64>(p, st);
-        case 128: return mmq_launch<TYPE, 128>(p, st);
-        default: return mmq_launch<TYPE, 256>(p, st);
+    if constexpr (TYPE != B200_TYPE_BF16) {
+        switch (mmq_bn(p.N)) {
+            case 32: return mmq_launch<TYPE, 32>(p, st);
+            case 64: return mmq_launch<TYPE, 64>(p, st);
+            case 128: return mmq_launch<TYPE, 128>(p, st);
+            default: return mmq_launch<TYPE, 256>(p, st);
+        }
     }
+    return B200_ERR_UNSUPPORTED;
 }
 
 
@@ -1028,7 +1063,7 @@ extern "C" int b200_mul_mat_q(int type, const void *W, size_t w_row_bytes, const
     const int bv = type_block_values(type);
     if (!(type == B200_TYPE_Q4_0 || type == B200_TYPE_Q8_0 || type == B200_TYPE_Q4_K || type == B200_TYPE_Q5_K || type == B200_TYPE_Q6_K ||
           type == B200_TYPE_Q4_1 || type == B200_TYPE_Q5_0 || type == B200_TYPE_Q5_1 || type == B200_TYPE_Q2_K || type == B200_TYPE_Q3_K ||
-          type == B200_TYPE_IQ4_NL || type == B200_TYPE_IQ4_XS)) {
+          type == B200_TYPE_IQ4_NL || type == B200_TYPE_IQ4_XS || type == B200_TYPE_BF16)) {
         set_error("b200_mul_mat_q: unsupported weight type %d", type);
         return B200_ERR_UNSUPPORTED;
     }
@@ -1037,8 +1072,8 @@ extern "C" int b200_mul_mat_q(int type, const void *W, size_t w_row_bytes, const
     if (M == 0 || N == 0) return B200_OK;
     const size_t row_bytes = (size_t)(K / bv) * type_block_bytes(type);
     if (w_row_bytes < row_bytes || (w_row_bytes & 1) || ((uintptr_t)W & 1)) { set_error("b200_mul_mat_q: weight stride/alignment"); return B200_ERR_INVALID; }
-    if ((type == B200_TYPE_Q4_K || type == B200_TYPE_Q5_K) && ((w_row_bytes & 15) || ((uintptr_t)W & 15))) {
-        set_error("b200_mul_mat_q: q4_K/q5_K rows must be 16-byte aligned");
+    if ((type == B200_TYPE_Q4_K || type == B200_TYPE_Q5_K || type == B200_TYPE_BF16) && ((w_row_bytes & 15) || ((uintptr_t)W & 15))) {
+        set_error("b200_mul_mat_q: q4_K / q5_K / bf16 rows must be 16-byte aligned");
         return B200_ERR_UNSUPPORTED;
     }
     if (X && (((uintptr_t)X & 15) || (x_stride & 3))) { set_error("b200_mul_mat_q: X must be 16-byte aligned with a row stride multiple of 4"); return B200_ERR_UNSUPPORTED; }
@@ -1072,6 +1107,7 @@ extern "C" int b200_mul_mat_q(int type, const void *W, size_t w_row_bytes, const
         case B200_TYPE_Q3_K: return mmq_dispatch_bn<B200_TYPE_Q3_K>(p, st);
         case B200_TYPE_IQ4_NL: return mmq_dispatch_bn<B200_TYPE_IQ4_NL>(p, st);
         case B200_TYPE_IQ4_XS: return mmq_dispatch_bn<B200_TYPE_IQ4_XS>(p, st);
+        case B200_TYPE_BF16: return mmq_dispatch_bn<B200_TYPE_BF16>(p, st);
     }
     return B200_ERR_UNSUPPORTED;
 }
