@@ -558,6 +558,205 @@ def product_arm(args, rank: int, world: int, local_rank: int) -> int:
     return 0
 
 
+
+# ------------------------------------------------------------------------------------------------ --design genesun
+# Prefill and decode of the Genesun design at layer shapes of real model sizes (random bf16 weights), beside the llama decoder
+# at equal width, depth and feed-forward size (Q4_K_M, the framework's flagship format).  Device time: the step's graph replayed
+# with its inputs resident, CUDA events on the backend stream, an L2 flush (256 MB memset) before every timed replay.
+DESIGN_SIZES = {
+    # width, (attention: heads, dim, rot_dim, vdim, kv_rank, q_rank), (mLSTM: heads, dim, vdim), ff
+    "w1024": (1024, (8, 64, 32, 64, 256, 384), (4, 128, 256), 2816),
+    "w2048": (2048, (16, 128, 64, 128, 512, 768), (4, 256, 512), 5632),
+    "w4096": (4096, (32, 128, 64, 128, 512, 1536), (8, 256, 512), 11008),
+}
+DESIGN_LAYERS, DESIGN_VOCAB, DESIGN_CTX, DESIGN_PP = 8, 32000, 1024, 512
+
+
+def genesun_config(size: str) -> dict:
+    import math
+    W, (h, d, r, v, kr, qr), (mh, md, mv), ff = DESIGN_SIZES[size]
+    rot = {"base": 10000.0, "dims": r, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    layers = []
+    for il in range(DESIGN_LAYERS):
+        k = il % 4
+        if k in (0, 3):
+            layers.append({"type": "mlstm", "mixer": {"heads": mh, "dim": md, "vdim": mv, "gate_cap": 15.0}, "mlp": None})
+        else:
+            mx = {"heads": h, "dim": d, "rot_dim": r, "vdim": v, "kv_rank": kr, "q_rank": qr, "scale": 1.0 / math.sqrt(d + r), "rot": rot}
+            if k == 2:
+                mx["kv_from"] = il - 1
+            layers.append({"type": "latent_attention", "mixer": mx, "mlp": {"kind": "dense", "ff": ff}})
+    return {"architecture": "Genesun", "width": W, "vocab": DESIGN_VOCAB, "norm": {"eps": 1e-6}, "layers": layers}
+
+
+def genesun_tensor_shapes(cfg: dict) -> dict:
+    W, V = cfg["width"], cfg["vocab"]
+    t = {"embed": (V, W), "head": (V, W), "final.norm": (W,)}
+    for i, L in enumerate(cfg["layers"]):
+        p, mx = f"l{i}.", L["mixer"]
+        H, D, Vd = mx["heads"], mx["dim"], mx["vdim"]
+        t.update({p + "norm1": (W,), p + "norm1b": (W,), p + "rg1": (W, W), p + "rg1.b": (W,), p + "dwa": (i + 2,)})
+        if L["type"] == "mlstm":
+            t.update({p + "mix.q": (H * D, W), p + "mix.k": (H * D, W), p + "mix.v": (H * Vd, W), p + "mix.g": (H * Vd, W), p + "mix.o": (W, H * Vd),
+                      p + "mix.norm": (H * Vd,), p + "mix.i": (H, W), p + "mix.i.b": (H,), p + "mix.f": (H, W), p + "mix.f.b": (H,)})
+        else:
+            R, KR, QR = mx["rot_dim"], mx["kv_rank"], mx["q_rank"]
+            t.update({p + "mix.dq": (QR, W), p + "mix.dq.norm": (QR,), p + "mix.uq": (H * (D + R), QR), p + "mix.uk": (H * D, KR), p + "mix.uv": (H * Vd, KR),
+                      p + "mix.sink": (H,), p + "mix.g": (H * Vd, W), p + "mix.o": (W, H * Vd)})
+            if "kv_from" not in mx:
+                t.update({p + "mix.dkv": (KR + R, W), p + "mix.dkv.norm": (KR,)})
+        if L["mlp"]:
+            ff = L["mlp"]["ff"]
+            t.update({p + "norm2": (W,), p + "norm2b": (W,), p + "rg2": (W, W), p + "rg2.b": (W,), p + "mlp.up": (ff, W), p + "mlp.down": (W, ff), p + "mlp.act": (4,)})
+    return t
+
+
+def genesun_random_tensors(cfg: dict, seed: int = 1):
+    """Random weights of the right shapes (one pool of N(0, 0.02) values cut into the matrices; vectors near their neutral value)."""
+    rng = np.random.default_rng(seed)
+    pool = (rng.standard_normal(1 << 24, dtype=np.float32) * 0.02)
+    pool_bits = ((pool.view(np.uint32) + 0x8000) >> 16).astype(np.uint16)
+    out, at = {}, 0
+    for name, shape in genesun_tensor_shapes(cfg).items():
+        n = int(np.prod(shape))
+        if len(shape) == 2 and name != "embed":
+            reps = -(-n // len(pool_bits))
+            bits = np.roll(pool_bits, at)[:n] if reps == 1 else np.tile(pool_bits, reps)[:n]
+            at = (at + 7919 * 13) % len(pool_bits)
+            out[name] = ("BF16", shape, bits.view(np.uint8))
+        elif name == "embed":
+            out[name] = ("F32", shape, np.resize(pool * 50, n).view(np.uint8))
+        else:
+            leaf = name.split(".")[-1]
+            v = np.full(n, 1.0, np.float32) if "norm" in leaf else np.zeros(n, np.float32)
+            if leaf == "dwa":
+                v[:] = 1.0 / n
+            if leaf == "act":
+                v[:] = [0.6, 0.3, 0.1, 0.0]
+            if name.endswith("f.b"):
+                v[:] = 3.0
+            out[name] = ("F32", shape, v.view(np.uint8))
+    return out
+
+
+def genesun_step_cost(cfg: dict, n_tokens: int, n_seq: int, ctx: int) -> dict:
+    """Algorithmic bytes (bf16 weights once, latent cache rows and recurrent state of the batch) and FLOPs of one step."""
+    W, V = cfg["width"], cfg["vocab"]
+    wparams = W * V  # head
+    cache = state = attn_flop = 0
+    for L in cfg["layers"]:
+        mx = L["mixer"]
+        H, D, Vd = mx["heads"], mx["dim"], mx["vdim"]
+        wparams += W * W + (2 * W * L["mlp"]["ff"] + W * W if L["mlp"] else 0)
+        if L["type"] == "mlstm":
+            wparams += W * (2 * H * D + 2 * H * Vd + 2 * H) + W * H * Vd
+            state += n_seq * H * D * Vd * 4 * 2
+        else:
+            R, KR, QR = mx["rot_dim"], mx["kv_rank"], mx["q_rank"]
+            wparams += W * QR + QR * H * (D + R) + H * D * KR + H * Vd * KR + 2 * W * H * Vd + (W * (KR + R) if "kv_from" not in mx else 0)
+            cache += n_seq * ctx * (KR + R) * 4
+            attn_flop += 2 * n_tokens * H * (ctx if n_tokens == n_seq else ctx // 2) * (2 * KR + R)
+    return {"weight_bytes": 2 * wparams, "cache_bytes": cache, "state_bytes": state, "flop": 2 * wparams * n_tokens + attn_flop}
+
+
+def design_leg(args) -> int:
+    import koboldcpp_b200.llama as LL
+    from koboldcpp_b200 import genesun as G
+    from koboldcpp_b200.engine import Engine
+    from koboldcpp_b200.lib import F16, check, lib
+    L = lib()
+    if L.b200_device_count() <= 0:
+        print("bench.py: no CUDA device and the product has no CPU path", file=sys.stderr)
+        return 2
+    hbm_gbs, _ = peaks()
+    try:
+        tfl = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()).get("bf16_tflops", 1590.0)
+    except Exception:
+        tfl = 1590.0
+    flush = C.c_void_p()
+    check(L.b200_malloc(C.byref(flush), 256 << 20))
+    e0, e1 = C.c_void_p(), C.c_void_p()
+    check(L.b200_event_create(C.byref(e0))); check(L.b200_event_create(C.byref(e1)))
+
+    def time_replay(model, stream, steps, warmup):
+        for _ in range(warmup):
+            model.replay()
+        total = 0.0
+        for _ in range(steps):
+            check(L.b200_memset(flush, 0, 256 << 20, stream))
+            check(L.b200_event_record(e0, stream))
+            model.replay()
+            check(L.b200_event_record(e1, stream))
+            check(L.b200_stream_synchronize(stream))
+            ms = C.c_float()
+            check(L.b200_event_elapsed_ms(e0, e1, C.byref(ms)))
+            total += ms.value
+        return total / steps
+
+    steps, warmup = max(3, min(args.steps, 20)), max(3, args.warmup)
+    rows = []
+    sizes = [s for s in DESIGN_SIZES if not args.design_sizes or s in args.design_sizes.split(",")]
+    for size in sizes:
+        cfg = genesun_config(size)
+        W = cfg["width"]
+        row = {"size": size, "width": W, "layers": DESIGN_LAYERS, "ctx": DESIGN_CTX}
+        m = G.build(cfg, genesun_random_tensors(cfg), dtype="bfloat16", n_ctx=8 * DESIGN_CTX + 256, n_seq_max=8, max_batch=DESIGN_PP)
+        eng = Engine(m)
+        rng = np.random.default_rng(0)
+        prompt = rng.integers(0, DESIGN_VOCAB, DESIGN_PP).tolist()
+        # prefill: one prompt of DESIGN_PP tokens
+        t0 = time.time()
+        eng.step([("p", prompt, [DESIGN_PP - 1])])
+        e2e_first = time.time() - t0
+        ms = time_replay(m, m.stream, steps, warmup)
+        cost = genesun_step_cost(cfg, DESIGN_PP, 1, DESIGN_PP)
+        row["genesun_prefill"] = {"tokens": DESIGN_PP, "ms": ms, "tok_s": DESIGN_PP / ms * 1e3, "tflops": cost["flop"] / ms / 1e9,
+                                  "of_measured_bf16": cost["flop"] / ms / 1e9 / tfl, "launches": m.stats()["n_kernels"], "first_call_s": e2e_first}
+        eng.finish("p")
+        # decode: 1 and 8 sequences at DESIGN_CTX tokens of context each
+        for nseq in (1, 8):
+            ids = [f"d{nseq}_{i}" for i in range(nseq)]
+            for rid in ids:
+                for a in range(0, DESIGN_CTX, DESIGN_PP):
+                    eng.step([(rid, rng.integers(0, DESIGN_VOCAB, DESIGN_PP).tolist(), [])])
+            t0 = time.time()
+            n_e2e = 8
+            for _ in range(n_e2e):
+                lg = eng.step([(rid, [5], [0]) for rid in ids])
+            e2e_ms = (time.time() - t0) / n_e2e * 1e3
+            ms = time_replay(m, m.stream, steps, warmup)
+            cost = genesun_step_cost(cfg, nseq, nseq, DESIGN_CTX)
+            byt = cost["weight_bytes"] + cost["cache_bytes"] + cost["state_bytes"]
+            row[f"genesun_decode_b{nseq}"] = {"ms": ms, "tok_s": nseq / ms * 1e3, "e2e_ms": e2e_ms, "e2e_tok_s": nseq / e2e_ms * 1e3, "alg_bytes": byt, "gbs": byt / ms / 1e6,
+                                              "of_measured_hbm": byt / ms / 1e6 / hbm_gbs, "launches": m.stats()["n_kernels"], "finite": bool(np.isfinite(lg).all())}
+            for rid in ids:
+                eng.finish(rid)
+        m.close()
+        # the llama decoder at equal width, depth and feed-forward size
+        _, (h, d, r, v, kr, qr), _, ff = DESIGN_SIZES[size]
+        shape = LL.ModelShape(f"llama-{size}", W, DESIGN_LAYERS, W // 128, W // 128, (ff + 255) // 256 * 256, DESIGN_VOCAB, "Q4_K_M")
+        lm = LL.LlamaModel(shape, DESIGN_CTX + 256, F16)
+        lm.init_random(seed=3)
+        lm.finalize(max_batch=DESIGN_PP)
+        lm.kv_fill_random(DESIGN_CTX, seed=7)
+        lm.decode(prompt, 0)
+        ms = time_replay(lm, lm.stream, steps, warmup)
+        lflop = 2 * DESIGN_PP * (shape.n_layer * (4 * W * W + 3 * W * shape.n_ff) + W * DESIGN_VOCAB) + 4 * DESIGN_PP * (DESIGN_PP // 2) * W * shape.n_layer
+        row["llama_prefill"] = {"tokens": DESIGN_PP, "ms": ms, "tok_s": DESIGN_PP / ms * 1e3, "tflops": lflop / ms / 1e9, "of_measured_bf16": lflop / ms / 1e9 / tfl,
+                                "launches": lm.stats()["n_kernels"]}
+        lm.kv_fill_random(DESIGN_CTX, seed=7)
+        lm.decode([5], DESIGN_CTX)
+        ms = time_replay(lm, lm.stream, steps, warmup)
+        byt = LL.weight_bytes_per_token(shape) + LL.kv_bytes_per_token(shape, DESIGN_CTX + 256, F16)
+        row["llama_decode_b1"] = {"ms": ms, "tok_s": 1e3 / ms, "alg_bytes": byt, "gbs": byt / ms / 1e6, "of_measured_hbm": byt / ms / 1e6 / hbm_gbs, "launches": lm.stats()["n_kernels"]}
+        lm.close()
+        rows.append(row)
+        print(json.dumps({"design_size": row}), file=sys.stderr, flush=True)
+    print(json.dumps({"design": "genesun", "beside": "llama Q4_K_M, equal width / depth / ff", "dtype": "bf16", "data": "synthetic", "steps": steps, "warmup": warmup,
+                      "timing": "CUDA events around the replayed step graph, 256 MB L2 flush before each", "sizes": rows}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -569,7 +768,12 @@ def main() -> int:
     ap.add_argument("--cpu-budget", type=float, default=18.0)
     ap.add_argument("--no-tp70", action="store_true", default=bool(os.environ.get("B200_BENCH_NO_TP70")),
                     help="skip the auxiliary 70B tensor-parallel leg (BASELINE.json configs[4])")
+    ap.add_argument("--design", default="", choices=["", "genesun"],
+                    help="instead of the round benchmark: prefill / decode of this design at real layer shapes beside the llama decoder at equal size")
+    ap.add_argument("--design-sizes", default="", help="comma-separated subset of " + ",".join(DESIGN_SIZES))
     args = ap.parse_args()
+    if args.design:
+        return design_leg(args)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

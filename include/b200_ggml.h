@@ -206,6 +206,14 @@ B200_API int b200_mul_mat_q(int type, const void *W, size_t w_row_bytes, const f
                             float *dst, int64_t dst_stride, int64_t K, int64_t M, int64_t N,
                             void *workspace, size_t workspace_bytes, b200_stream_t stream);
 
+/* Dense bf16 weights: b200_mul_mat_q also takes B200_TYPE_BF16 (rows 16-byte aligned, K a multiple of 64).  A batch of n_batch
+ * independent products of one shape (the per-head matrices of an attention layer) runs as ONE launch: product b reads
+ * W + b * w_batch_bytes and X + b * x_batch floats and writes dst + b * dst_batch floats.  Workspace: n_batch times
+ * b200_mul_mat_q_workspace_bytes(B200_TYPE_BF16, K, M, N). */
+B200_API int b200_mul_mat_bf16_batched(const void *W, size_t w_row_bytes, size_t w_batch_bytes, const float *X, int64_t x_stride, int64_t x_batch, float *dst,
+                                       int64_t dst_stride, int64_t dst_batch, int64_t K, int64_t M, int64_t N, int32_t n_batch, void *workspace,
+                                       size_t workspace_bytes, b200_stream_t stream);
+
 /* ---- (a10-a12) FLASH_ATTN_EXT -----------------------------------------------------------------------
  * replaces: ggml_cuda_flash_attn_ext -> flash_attn_vec_ext_f16/f32 + flash_attn_combine_results (decode) and
  * flash_attn_ext_f16 (wmma, prefill) incl. the full-tensor dequantisation of a quantised KV cache,

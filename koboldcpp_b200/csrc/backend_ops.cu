@@ -349,6 +349,12 @@ static void run_mul_mat(ExecCtx &x, const ggml_tensor *n) {
             // prompt batches over dense bf16 weights: the tensor-core GEMM, one launch per (i2, i3) slice of a per-head product
             const int64_t K = w->ne[0], M = w->ne[1], N = a->ne[1];
             const int64_t r2 = a->ne[2] / w->ne[2], r3 = a->ne[3] / w->ne[3];
+            if (a->ne[2] > 1 && a->ne[3] == 1 && w->ne[2] == a->ne[2] && a->ne[2] <= 65535) {  // one matrix per head: one batched launch
+                B200_CHECK_RC(b200_mul_mat_bf16_batched(w->data, w->nb[1], w->nb[2], (const float *)a->data, (int64_t)(a->nb[1] / 4), (int64_t)(a->nb[2] / 4), (float *)n->data,
+                                                        (int64_t)(n->nb[1] / 4), (int64_t)(n->nb[2] / 4), K, M, N, (int32_t)a->ne[2], x.scratch, x.scratch_bytes, x.stream));
+                x.launches += 2;
+                return;
+            }
             for (int64_t i13 = 0; i13 < a->ne[3]; i13++) {
                 for (int64_t i12 = 0; i12 < a->ne[2]; i12++) {
                     const char *ws = (const char *)w->data + (i12 / r2) * w->nb[2] + (i13 / r3) * w->nb[3];
@@ -463,7 +469,11 @@ static bool bf16_gemm_ok(const ggml_tensor *n) {
 }
 
 size_t node_scratch_bytes(const ggml_tensor *n) {
-    if (bf16_gemm_ok(n)) return b200_mul_mat_q_workspace_bytes(n->src[0]->type, n->src[0]->ne[0], n->src[0]->ne[1], n->src[1]->ne[1]);
+    if (bf16_gemm_ok(n)) {
+        const ggml_tensor *w = n->src[0], *a = n->src[1];
+        const size_t one = b200_mul_mat_q_workspace_bytes(w->type, w->ne[0], w->ne[1], a->ne[1]);
+        return (a->ne[2] > 1 && a->ne[3] == 1 && w->ne[2] == a->ne[2]) ? one * (size_t)a->ne[2] : one;
+    }
     if (n->op == GGML_OP_MUL_MAT_ID && n->src[0] && n->src[2] && n->src[2]->ne[0] * n->src[2]->ne[1] > B200_GEMV_MAX_JOBS)
         return b200_mul_mat_id_q_workspace_bytes(n->src[0]->type, n->src[0]->ne[0], n->src[0]->ne[1], n->src[2]->ne[0], n->src[2]->ne[1], (int32_t)n->src[0]->ne[2]);
     if (n->op != GGML_OP_MUL_MAT || !n->src[0] || !n->src[1] || !is_quantized(n->src[0]->type) || n->src[1]->ne[1] <= 8) return 0;

@@ -37,12 +37,15 @@ __global__ void latent_kv_store_kernel(const float *__restrict__ dkv, int64_t dk
     }
 }
 
-// One CTA per (token, head); warps stride over the cells, each keeping an online softmax and a latent accumulator that are
-// merged through shared memory at the end.  NL = ceil(kv_rank / 32), NR = ceil(rot_dim / 32): values per lane.
-constexpr int LA_WARPS = 4;
-template <int NL, int NR>
-__global__ void __launch_bounds__(LA_WARPS * 32) latent_attn_kernel(const b200_latent_attn_args a) {
-    extern __shared__ float smem[];  // [LA_WARPS][kv_rank] accumulators, then m[LA_WARPS], l[LA_WARPS]
+// One CTA per (token, head); its warps stride over the cells, each keeping an online softmax and a latent accumulator that are
+// merged through shared memory at the end.  A warp takes LA_UNROLL cells per round: the visibility tests and the row loads of
+// the whole round are issued before the first dot product, so a round pays the L2 latency once instead of once per cell.
+// WARPS is 4 for prompt batches (many CTAs) and 16 when there are few (token, head) pairs (decode), where the cells of one
+// pair are the only parallelism there is.  NL = ceil(kv_rank / 32), NR = ceil(rot_dim / 32): values per lane.
+constexpr int LA_UNROLL = 4;
+template <int NL, int NR, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) latent_attn_kernel(const b200_latent_attn_args a) {
+    extern __shared__ float smem[];  // [WARPS][kv_rank] accumulators, then m[WARPS], l[WARPS]
     const int t = blockIdx.x, h = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int KR = a.kv_rank, R = a.rot_dim;
@@ -56,59 +59,90 @@ __global__ void __launch_bounds__(LA_WARPS * 32) latent_attn_kernel(const b200_l
     const int seq = a.tok_seq[t], pos = a.tok_pos[t];
     const int lo = a.window > 0 ? pos - a.window : INT_MIN;
     float m = -INFINITY, l = 0.f;
-    for (int c = warp; c < a.n_kv; c += LA_WARPS) {
-        const int cp = a.cell_pos[c];
-        if (a.cell_seq[c] != seq || cp > pos || cp <= lo) continue;  // warp-uniform
-        const float *row = a.cache + (int64_t)c * a.cache_stride;
-        float rv[NL], s = 0.f;
+    for (int c0 = warp * LA_UNROLL; c0 < a.n_kv; c0 += WARPS * LA_UNROLL) {
+        bool vis[LA_UNROLL];
+        float rv[LA_UNROLL][NL], rr[LA_UNROLL][NR];
 #pragma unroll
-        for (int i = 0; i < NL; i++) { const int j = lane + 32 * i; rv[i] = j < KR ? row[j] : 0.f; s += q1[i] * rv[i]; }
+        for (int u = 0; u < LA_UNROLL; u++) {
+            const int c = c0 + u;
+            const int cp = c < a.n_kv ? a.cell_pos[c] : -1;
+            vis[u] = c < a.n_kv && a.cell_seq[c] == seq && cp <= pos && cp > lo;  // warp-uniform
+        }
 #pragma unroll
-        for (int i = 0; i < NR; i++) { const int j = lane + 32 * i; s += q2[i] * (j < R ? row[KR + j] : 0.f); }
-        s = warp_sum(s);
-        const float mn = fmaxf(m, s);
-        const float corr = expf(m - mn), p = expf(s - mn);  // m = -inf at the first cell: corr = 0
-        l = l * corr + p;
+        for (int u = 0; u < LA_UNROLL; u++) {
+            if (!vis[u]) continue;
+            const float *row = a.cache + (int64_t)(c0 + u) * a.cache_stride;
 #pragma unroll
-        for (int i = 0; i < NL; i++) acc[i] = acc[i] * corr + p * rv[i];
-        m = mn;
+            for (int i = 0; i < NL; i++) { const int j = lane + 32 * i; rv[u][i] = j < KR ? row[j] : 0.f; }
+#pragma unroll
+            for (int i = 0; i < NR; i++) { const int j = lane + 32 * i; rr[u][i] = j < R ? row[KR + j] : 0.f; }
+        }
+        float s[LA_UNROLL];
+#pragma unroll
+        for (int u = 0; u < LA_UNROLL; u++) {
+            s[u] = 0.f;
+            if (!vis[u]) continue;
+#pragma unroll
+            for (int i = 0; i < NL; i++) s[u] += q1[i] * rv[u][i];
+#pragma unroll
+            for (int i = 0; i < NR; i++) s[u] += q2[i] * rr[u][i];
+        }
+#pragma unroll
+        for (int u = 0; u < LA_UNROLL; u++) if (vis[u]) s[u] = warp_sum(s[u]);
+#pragma unroll
+        for (int u = 0; u < LA_UNROLL; u++) {
+            if (!vis[u]) continue;
+            const float mn = fmaxf(m, s[u]);
+            const float corr = expf(m - mn), p = expf(s[u] - mn);  // m = -inf at the first cell: corr = 0
+            l = l * corr + p;
+#pragma unroll
+            for (int i = 0; i < NL; i++) acc[i] = acc[i] * corr + p * rv[u][i];
+            m = mn;
+        }
     }
-    float *sacc = smem + (size_t)warp * KR, *sm = smem + (size_t)LA_WARPS * KR, *sl = sm + LA_WARPS;
+    float *sacc = smem + (size_t)warp * KR, *sm = smem + (size_t)WARPS * KR, *sl = sm + WARPS;
 #pragma unroll
     for (int i = 0; i < NL; i++) { const int j = lane + 32 * i; if (j < KR) sacc[j] = acc[i]; }
     if (lane == 0) { sm[warp] = m; sl[warp] = l; }
     __syncthreads();
     const float sink = a.sink ? a.sink[h] : -INFINITY;
     float M = sink;
-#pragma unroll
-    for (int w = 0; w < LA_WARPS; w++) M = fmaxf(M, sm[w]);
-    float L = a.sink ? expf(sink - M) : 0.f, f[LA_WARPS];
-#pragma unroll
-    for (int w = 0; w < LA_WARPS; w++) { f[w] = sm[w] == -INFINITY ? 0.f : expf(sm[w] - M); L += sl[w] * f[w]; }
+    for (int w = 0; w < WARPS; w++) M = fmaxf(M, sm[w]);
+    float L = a.sink ? expf(sink - M) : 0.f;
+    for (int w = 0; w < WARPS; w++) if (sm[w] != -INFINITY) L += sl[w] * expf(sm[w] - M);
+    __syncthreads();
+    if (threadIdx.x < WARPS) sl[threadIdx.x] = sm[threadIdx.x] == -INFINITY ? 0.f : expf(sm[threadIdx.x] - M);  // the warp's weight in the merge
+    __syncthreads();
     const float inv = 1.0f / L;
     float *out = a.dst + (int64_t)h * a.dst_s_head + (int64_t)t * a.dst_s_tok;
     for (int j = threadIdx.x; j < KR; j += blockDim.x) {
         float o = 0.f;
-#pragma unroll
-        for (int w = 0; w < LA_WARPS; w++) o += smem[(size_t)w * KR + j] * f[w];
+        for (int w = 0; w < WARPS; w++) o += smem[(size_t)w * KR + j] * sl[w];
         out[j] = o * inv;
     }
 }
 
-template <int NL>
-static int launch_latent_attn(const b200_latent_attn_args *a, cudaStream_t st) {
+template <int NL, int NR, int WARPS>
+static int launch_latent_attn3(const b200_latent_attn_args *a, cudaStream_t st) {
     const dim3 grid((unsigned)a->n_tokens, (unsigned)a->n_head);
-    const size_t smem = ((size_t)LA_WARPS * a->kv_rank + 2 * LA_WARPS) * 4;
-    const int nr = (a->rot_dim + 31) / 32;
-#define B200_LA_LAUNCH(NR)                                                                                                              \
-    do {                                                                                                                                \
-        if (smem > 48 * 1024) B200_CUDA_TRY(cudaFuncSetAttribute(latent_attn_kernel<NL, NR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-        latent_attn_kernel<NL, NR><<<grid, LA_WARPS * 32, smem, st>>>(*a);                                                              \
-    } while (0)
-    if (nr <= 1) B200_LA_LAUNCH(1); else if (nr <= 2) B200_LA_LAUNCH(2); else B200_LA_LAUNCH(4);
-#undef B200_LA_LAUNCH
+    const size_t smem = ((size_t)WARPS * a->kv_rank + 2 * WARPS) * 4;
+    if (smem > 48 * 1024) B200_CUDA_TRY(cudaFuncSetAttribute(latent_attn_kernel<NL, NR, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    latent_attn_kernel<NL, NR, WARPS><<<grid, WARPS * 32, smem, st>>>(*a);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
+}
+template <int NL, int NR>
+static int launch_latent_attn2(const b200_latent_attn_args *a, cudaStream_t st) {
+    // few (token, head) pairs: 16 warps share the cells of a pair
+    if ((int64_t)a->n_tokens * a->n_head < 2 * 148 && a->n_kv > 64) return launch_latent_attn3<NL, NR, 16>(a, st);
+    return launch_latent_attn3<NL, NR, 4>(a, st);
+}
+template <int NL>
+static int launch_latent_attn(const b200_latent_attn_args *a, cudaStream_t st) {
+    const int nr = (a->rot_dim + 31) / 32;
+    if (nr <= 1) return launch_latent_attn2<NL, 1>(a, st);
+    if (nr <= 2) return launch_latent_attn2<NL, 2>(a, st);
+    return launch_latent_attn2<NL, 4>(a, st);
 }
 
 }  // namespace b200

@@ -369,9 +369,12 @@ struct Dequant64<B200_TYPE_Q6_K, G> {  // u8 ql[128], u8 qh[64], i8 scales[16], 
 };
 
 // ---------------------------------------------------------------- activation pre-pass: f32 [N][K] -> bf16 [N_pad][K] (pad rows zero)
-__global__ void mmq_x_to_bf16_kernel(const float *__restrict__ x, int64_t x_stride, int64_t K, int64_t N, int64_t n_pad, __nv_bfloat16 *__restrict__ out) {
+__global__ void mmq_x_to_bf16_kernel(const float *__restrict__ x, int64_t x_stride, int64_t K, int64_t N, int64_t n_pad, __nv_bfloat16 *__restrict__ out,
+                                     int64_t x_batch = 0) {
     const int64_t i4 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;  // float4 index within a row
     const int64_t n = blockIdx.y;
+    x += (int64_t)blockIdx.z * x_batch;            // a batch of independent products: blockIdx.z
+    out += (int64_t)blockIdx.z * n_pad * K;
     if (i4 * 4 >= K) return;
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
     if (n < N) v = __ldg(reinterpret_cast<const float4 *>(x + n * x_stride) + i4);
@@ -395,6 +398,11 @@ struct MmqParams {
     // split-K (mmq_tc2_kernel, not grouped): blockIdx.z owns a contiguous share of the 256-value groups and ADDS its tile into a
     // zeroed dst (red.global.add.f32).  Only 1 or 2: the sum of two partials does not depend on their arrival order.
     int ksplit;
+    // batch of independent products of one shape (not grouped, no split-K): blockIdx.z picks the product; W advances by
+    // w_batch_bytes, dst by dst_batch floats, the bf16 activations by n_pad rows
+    int n_batch;
+    size_t w_batch_bytes;
+    int64_t dst_batch, n_pad;
 };
 
 template <int TYPE, int BN>
@@ -706,8 +714,11 @@ __global__ void __launch_bounds__(MQ2_THREADS, 1) mmq_tc2_kernel(const __grid_co
     const int nsb_all = (int)(p.K / (MQ_BK * KPG));
     // split-K: this CTA's groups [sb0, sb0 + nsb)
     const int ksplit = GROUPED ? 1 : p.ksplit;
-    const int sb0 = (int)(((int64_t)blockIdx.z * nsb_all) / ksplit);
-    const int nsb = (int)(((int64_t)(blockIdx.z + 1) * nsb_all) / ksplit) - sb0, nkb = nsb * KPG;
+    const bool batched = !GROUPED && p.n_batch > 1;
+    const int zk = batched ? 0 : (int)blockIdx.z, zb = batched ? (int)blockIdx.z : 0;
+    if (batched) Wbase += (size_t)zb * p.w_batch_bytes;
+    const int sb0 = (int)(((int64_t)zk * nsb_all) / ksplit);
+    const int nsb = (int)(((int64_t)(zk + 1) * nsb_all) / ksplit) - sb0, nkb = nsb * KPG;
 
     if (tid == 0) {
         for (int s = 0; s < MQ2_STAGES; s++) { mbar_init(&full_bar[s], MQ_PRODUCERS + 1); mbar_init(&empty_bar[s], 1); }
@@ -808,7 +819,7 @@ __global__ void __launch_bounds__(MQ2_THREADS, 1) mmq_tc2_kernel(const __grid_co
         }
         mbar_wait(&tmem_full_bar, 0u);
         tc_fence_after();
-        float *drow = p.dst + m;
+        float *drow = p.dst + m + (batched ? (int64_t)zb * p.dst_batch : 0);
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
             float v[32];
@@ -853,7 +864,7 @@ __global__ void __launch_bounds__(MQ2_THREADS, 1) mmq_tc2_kernel(const __grid_co
                 const int s = kb % MQ2_STAGES;
                 mbar_wait(&empty_bar[s], ((unsigned)(kb / MQ2_STAGES) & 1u) ^ 1u);
                 mbar_expect_tx(&full_bar[s], (unsigned)B_BYTES);
-                tma_load_2d(smem + (size_t)s * STAGE_BYTES + A_BYTES, &tmB, (sb0 * KPG + kb) * MQ_BK, (int)n0, &full_bar[s]);
+                tma_load_2d(smem + (size_t)s * STAGE_BYTES + A_BYTES, &tmB, (sb0 * KPG + kb) * MQ_BK, (int)n0 + (batched ? zb * (int)p.n_pad : 0), &full_bar[s]);
             }
         }
     }
@@ -911,7 +922,7 @@ static int mmq2_launch(const MmqParams &p, int64_t n_pad, cudaStream_t st, unsig
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) { set_error("b200_mul_mat_q: cuTensorMapEncodeTiled not available"); return B200_ERR_CUDA; }
     TmapBytes tm;
-    const unsigned long long gdim[2] = {(unsigned long long)p.K, (unsigned long long)n_pad};
+    const unsigned long long gdim[2] = {(unsigned long long)p.K, (unsigned long long)n_pad * (unsigned long long)(p.n_batch > 1 ? p.n_batch : 1)};
     const unsigned long long gstr[1] = {(unsigned long long)p.K * 2};
     const unsigned box[2] = {(unsigned)MQ_BK, (unsigned)BN};
     const unsigned estr[2] = {1, 1};
@@ -925,7 +936,9 @@ static int mmq2_launch(const MmqParams &p, int64_t n_pad, cudaStream_t st, unsig
         // fewer tiles than half the SMs (M = 4096 x N = 512: 64 CTAs, every one bound by its own 128 dequantising threads): two
         // CTAs share a tile's K range and add into a zeroed dst.  Two partials only: the sum is independent of the arrival order.
         static const bool no_split = getenv("B200_MMQ_NO_SPLITK") != nullptr;
-        if (!no_split && (int64_t)grid.x * grid.y * 2 <= 148 && p.K >= 2048) {
+        if (p.n_batch > 1) {
+            grid.z = (unsigned)p.n_batch;
+        } else if (!no_split && (int64_t)grid.x * grid.y * 2 <= 148 && p.K >= 2048) {
             q.ksplit = 2;
             grid.z = 2;
             if (p.dst_stride == p.M) B200_CUDA_TRY(cudaMemsetAsync(p.dst, 0, (size_t)p.M * p.N * sizeof(float), st));
@@ -1094,6 +1107,7 @@ extern "C" int b200_mul_mat_q(int type, const void *W, size_t w_row_bytes, const
     MmqParams p;
     p.W = (const unsigned char *)W; p.w_row_bytes = w_row_bytes; p.Xb = xb; p.dst = dst; p.dst_stride = dst_stride; p.K = K; p.M = M; p.N = N;
     p.tile_tab = nullptr; p.row_dst = nullptr; p.expert_bytes = 0;
+    p.n_batch = 1; p.w_batch_bytes = 0; p.dst_batch = 0; p.n_pad = n_pad;
     switch (type) {
         case B200_TYPE_Q4_0: return mmq_dispatch_bn<B200_TYPE_Q4_0>(p, st);
         case B200_TYPE_Q8_0: return mmq_dispatch_bn<B200_TYPE_Q8_0>(p, st);
@@ -1110,6 +1124,32 @@ extern "C" int b200_mul_mat_q(int type, const void *W, size_t w_row_bytes, const
         case B200_TYPE_BF16: return mmq_dispatch_bn<B200_TYPE_BF16>(p, st);
     }
     return B200_ERR_UNSUPPORTED;
+}
+
+// A batch of independent products of one shape over dense bf16 weights (the per-head matrices of an attention layer) in ONE
+// launch: product b reads W + b * w_batch_bytes and X + b * x_batch and writes dst + b * dst_batch.
+extern "C" int b200_mul_mat_bf16_batched(const void *W, size_t w_row_bytes, size_t w_batch_bytes, const float *X, int64_t x_stride, int64_t x_batch, float *dst,
+                                         int64_t dst_stride, int64_t dst_batch, int64_t K, int64_t M, int64_t N, int32_t n_batch, void *workspace,
+                                         size_t workspace_bytes, b200_stream_t stream) {
+    if (!W || !X || !dst || n_batch < 1 || n_batch > 65535) { set_error("b200_mul_mat_bf16_batched: bad argument"); return B200_ERR_INVALID; }
+    if (K <= 0 || K % MQ_BK || M <= 0 || N <= 0) { set_error("b200_mul_mat_bf16_batched: K=%lld must be a positive multiple of %d", (long long)K, MQ_BK); return B200_ERR_UNSUPPORTED; }
+    if (((uintptr_t)W | w_row_bytes | w_batch_bytes | (uintptr_t)X) & 15 || (x_stride & 3) || (x_batch & 3)) { set_error("b200_mul_mat_bf16_batched: operands must be 16-byte aligned"); return B200_ERR_UNSUPPORTED; }
+    const int64_t n_pad = mmq_n_pad(N);
+    const size_t need = (size_t)n_pad * (size_t)K * 2 * (size_t)n_batch + 256;
+    if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 15) || n_pad * n_batch > 0x7fffffff) {
+        set_error("b200_mul_mat_bf16_batched: workspace of %zu bytes (16-byte aligned) required, %zu given", need, workspace_bytes);
+        return B200_ERR_INVALID;
+    }
+    const cudaStream_t st = (cudaStream_t)stream;
+    __nv_bfloat16 *xb = (__nv_bfloat16 *)workspace;
+    dim3 g1((unsigned)((K / 4 + 255) / 256), (unsigned)n_pad, (unsigned)n_batch);
+    mmq_x_to_bf16_kernel<<<g1, 256, 0, st>>>(X, x_stride, K, N, n_pad, xb, x_batch);
+    B200_CUDA_TRY(cudaGetLastError());
+    MmqParams p;
+    p.W = (const unsigned char *)W; p.w_row_bytes = w_row_bytes; p.Xb = xb; p.dst = dst; p.dst_stride = dst_stride; p.K = K; p.M = M; p.N = N;
+    p.tile_tab = nullptr; p.row_dst = nullptr; p.expert_bytes = 0;
+    p.n_batch = n_batch; p.w_batch_bytes = w_batch_bytes; p.dst_batch = dst_batch; p.n_pad = n_pad;
+    return mmq_dispatch_bn<B200_TYPE_BF16>(p, st);
 }
 
 extern "C" size_t b200_mul_mat_id_q_workspace_bytes(int type, int64_t K, int64_t M, int64_t n_used, int64_t T, int32_t n_expert) {
@@ -1167,6 +1207,7 @@ extern "C" int b200_mul_mat_id_q(int type, const void *as, size_t w_row_bytes, s
     MmqParams p;
     p.W = (const unsigned char *)as; p.w_row_bytes = w_row_bytes; p.Xb = xb; p.dst = dst; p.dst_stride = 0; p.K = K; p.M = M; p.N = n_rows;
     p.tile_tab = t.tile_tab; p.row_dst = t.row_dst; p.expert_bytes = expert_bytes;
+    p.n_batch = 1; p.w_batch_bytes = 0; p.dst_batch = 0; p.n_pad = 0;
     switch (type) {
         case B200_TYPE_Q4_0: return mid_dispatch_bn<B200_TYPE_Q4_0>(p, bn, n_rows, (unsigned)max_tiles, st);
         case B200_TYPE_Q8_0: return mid_dispatch_bn<B200_TYPE_Q8_0>(p, bn, n_rows, (unsigned)max_tiles, st);

@@ -631,52 +631,67 @@ __global__ void mul_mat_float_kernel(TD w, TD x, TD dst) {
 }
 
 
-// Dense bf16 weights, 1..8 activation columns (decode): HBM-bound on the weight stream.  One warp per output row, 16-byte weight
-// loads (8 values per lane and step, two steps in flight), f32 activations from L1 / L2, f32 accumulation, every column from one
-// read of the row.
-template <int NC>
-__global__ void __launch_bounds__(128) gemv_bf16_kernel(const unsigned char *__restrict__ W, int64_t w_row_bytes, const float *__restrict__ X, int64_t x_stride,
-                                                        float *__restrict__ dst, int64_t dst_stride, int64_t K, int64_t M) {
-    const int64_t m = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+// Dense bf16 weights, 1..8 activation columns (decode): HBM-bound on the weight stream.  A warp owns RPW output rows at a time
+// (two when there are several columns, so an activation value read from L1 meets two weights), 16-byte weight loads that do not
+// allocate in L1 (the activations stay there), f32 activations, f32 accumulation, every column from one read of the row.
+// blockIdx.y walks a batch of independent products (the per-head matrices of an attention layer).
+__device__ __forceinline__ uint4 ld_stream16(const uint4 *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+template <int NC, int RPW>
+__global__ void __launch_bounds__(128) gemv_bf16_kernel(const unsigned char *__restrict__ W, int64_t w_row_bytes, int64_t w_batch_bytes, const float *__restrict__ X,
+                                                        int64_t x_stride, int64_t x_batch, float *__restrict__ dst, int64_t dst_stride, int64_t dst_batch, int64_t K,
+                                                        int64_t M) {
+    const int64_t m0 = ((int64_t)blockIdx.x * 4 + (threadIdx.x >> 5)) * RPW;
     const int lane = threadIdx.x & 31;
-    if (m >= M) return;
-    const uint4 *wr = reinterpret_cast<const uint4 *>(W + m * w_row_bytes);
-    float acc[NC];
+    if (m0 >= M) return;
+    W += (int64_t)blockIdx.y * w_batch_bytes; X += (int64_t)blockIdx.y * x_batch; dst += (int64_t)blockIdx.y * dst_batch;
+    const uint4 *wr[RPW];
 #pragma unroll
-    for (int c = 0; c < NC; c++) acc[c] = 0.f;
+    for (int r = 0; r < RPW; r++) wr[r] = reinterpret_cast<const uint4 *>(W + (m0 + r < M ? m0 + r : m0) * w_row_bytes);
+    float acc[RPW][NC];
+#pragma unroll
+    for (int r = 0; r < RPW; r++)
+#pragma unroll
+        for (int c = 0; c < NC; c++) acc[r][c] = 0.f;
     const int64_t nv = K / 8;
-    for (int64_t i = lane; i < nv; i += 64) {
-        const bool two = i + 32 < nv;
-        const uint4 a = __ldg(wr + i);
-        const uint4 b = two ? __ldg(wr + i + 32) : make_uint4(0u, 0u, 0u, 0u);
-        const unsigned wa[4] = {a.x, a.y, a.z, a.w}, wb[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll 2
+    for (int64_t i = lane; i < nv; i += 32) {
+        uint4 a[RPW];
+#pragma unroll
+        for (int r = 0; r < RPW; r++) a[r] = ld_stream16(wr[r] + i);
 #pragma unroll
         for (int c = 0; c < NC; c++) {
             const float4 *xa = reinterpret_cast<const float4 *>(X + c * x_stride + i * 8);
             const float4 x0 = xa[0], x1 = xa[1];
             const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
 #pragma unroll
-            for (int j = 0; j < 4; j++) acc[c] += __uint_as_float(wa[j] << 16) * xs[2 * j] + __uint_as_float(wa[j] & 0xffff0000u) * xs[2 * j + 1];
-            if (two) {
-                const float4 y0 = xa[64], y1 = xa[65];
-                const float ys[8] = {y0.x, y0.y, y0.z, y0.w, y1.x, y1.y, y1.z, y1.w};
+            for (int r = 0; r < RPW; r++) {
+                const unsigned wa[4] = {a[r].x, a[r].y, a[r].z, a[r].w};
 #pragma unroll
-                for (int j = 0; j < 4; j++) acc[c] += __uint_as_float(wb[j] << 16) * ys[2 * j] + __uint_as_float(wb[j] & 0xffff0000u) * ys[2 * j + 1];
+                for (int j = 0; j < 4; j++) acc[r][c] += __uint_as_float(wa[j] << 16) * xs[2 * j] + __uint_as_float(wa[j] & 0xffff0000u) * xs[2 * j + 1];
             }
         }
     }
 #pragma unroll
-    for (int c = 0; c < NC; c++) {
-        const float v = warp_sum(acc[c]);
-        if (lane == 0) dst[c * dst_stride + m] = v;
-    }
+    for (int r = 0; r < RPW; r++)
+#pragma unroll
+        for (int c = 0; c < NC; c++) {
+            const float v = warp_sum(acc[r][c]);
+            if (lane == 0 && m0 + r < M) dst[c * dst_stride + m0 + r] = v;
+        }
 }
 
 template <int NC>
 static void launch_gemv_bf16(const b200_tensor *w, const b200_tensor *x, const b200_tensor *dst, cudaStream_t st) {
-    const int64_t M = w->ne[1];
-    gemv_bf16_kernel<NC><<<(unsigned)((M + 3) / 4), 128, 0, st>>>((const unsigned char *)w->data, (int64_t)w->nb[1], (const float *)x->data, (int64_t)(x->nb[1] / 4),
-                                                               (float *)dst->data, (int64_t)(dst->nb[1] / 4), w->ne[0], M);
+    const int64_t M = w->ne[1], nb = x->ne[2];
+    const int64_t wb = w->ne[2] > 1 ? (int64_t)w->nb[2] : 0;
+    constexpr int RPW = NC >= 3 ? 2 : 1;
+    const dim3 grid((unsigned)((M + 4 * RPW - 1) / (4 * RPW)), (unsigned)nb);
+    gemv_bf16_kernel<NC, RPW><<<grid, 128, 0, st>>>((const unsigned char *)w->data, (int64_t)w->nb[1], wb, (const float *)x->data, (int64_t)(x->nb[1] / 4),
+                                                    (int64_t)(x->nb[2] / 4), (float *)dst->data, (int64_t)(dst->nb[1] / 4), (int64_t)(dst->nb[2] / 4), w->ne[0], M);
 }
 
 static unsigned grid1d(int64_t n, int block) { return (unsigned)((n + block - 1) / block); }
@@ -971,8 +986,8 @@ extern "C" int b200_op_mul_mat_float(const b200_tensor *w, const b200_tensor *x,
     const int64_t total = nelements(dst);
     if (total == 0) return B200_OK;
     // decode over dense bf16 weights: the vectorised GEMV (plain 2-D operands, 16-byte aligned rows)
-    if (w->type == B200_TYPE_BF16 && x->ne[1] <= 8 && x->ne[2] == 1 && x->ne[3] == 1 && w->ne[2] == 1 && w->ne[3] == 1 && dst->nb[0] == 4 && w->ne[0] % 8 == 0 &&
-        (((uintptr_t)w->data | w->nb[1] | (uintptr_t)x->data | x->nb[1]) & 15) == 0 && (dst->nb[1] & 3) == 0) {
+    if (w->type == B200_TYPE_BF16 && x->ne[1] <= 8 && x->ne[3] == 1 && w->ne[3] == 1 && (w->ne[2] == 1 || w->ne[2] == x->ne[2]) && x->ne[2] <= 65535 && dst->nb[0] == 4 &&
+        w->ne[0] % 8 == 0 && (((uintptr_t)w->data | w->nb[1] | w->nb[2] | (uintptr_t)x->data | x->nb[1] | x->nb[2]) & 15) == 0 && ((dst->nb[1] | dst->nb[2]) & 3) == 0) {
         const cudaStream_t st = (cudaStream_t)stream;
         switch (x->ne[1]) {
             case 1: launch_gemv_bf16<1>(w, x, dst, st); break;

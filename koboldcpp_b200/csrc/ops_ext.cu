@@ -70,6 +70,76 @@ __global__ void polynorm_kernel(TD x, const float *__restrict__ coef, TD dst, fl
     }
 }
 
+
+// Rows of up to blockDim * VPT values stay in registers: every load of the row (and of its gate) is issued before the first
+// reduction, so a row costs one memory latency for the statistics and one for the weight / residual, whatever its length.
+template <int KIND, bool GATE, int VPT>
+__global__ void __launch_bounds__(1024) norm_reg_kernel(TD x, const float *__restrict__ w, int64_t w_period, TD gate, const float *__restrict__ gate_bias, TD res, bool has_res, TD dst,
+                                float eps) {
+    __shared__ float sh[32];
+    const int64_t r = blockIdx.x;
+    const float *xr = (const float *)row_ptr(x, r);
+    float *yr = (float *)row_ptr(dst, r);
+    const float *gr = GATE ? (const float *)row_ptr(gate, r) : nullptr;
+    const float *rr = has_res ? (const float *)row_ptr(res, r) : nullptr;
+    const float *wr = w ? w + (r % w_period) * x.ne[0] : nullptr;
+    const int n = (int)x.ne[0];
+    float v[VPT], g[VPT], wv[VPT], rv[VPT];
+#pragma unroll
+    for (int k = 0; k < VPT; k++) {
+        const int i = threadIdx.x + k * blockDim.x;
+        v[k] = i < n ? xr[i] : 0.f;
+        if (GATE) g[k] = i < n ? gr[i] + (gate_bias ? gate_bias[i] : 0.f) : 0.f;
+        wv[k] = (wr && i < n) ? wr[i] : 1.f;
+        rv[k] = (rr && i < n) ? rr[i] : 0.f;
+    }
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPT; k++) {
+        if (GATE) v[k] *= sigmoidf_(g[k]);
+        s += KIND == B200_NORM_RMS ? v[k] * v[k] : v[k];
+    }
+    float mean = 0.f, var;
+    if (KIND == B200_NORM_RMS) {
+        var = block_sum(s, sh) / (float)n;
+    } else {
+        mean = block_sum(s, sh) / (float)n;
+        float q = 0.f;
+#pragma unroll
+        for (int k = 0; k < VPT; k++) { const float d = threadIdx.x + k * blockDim.x < n ? v[k] - mean : 0.f; q += d * d; }
+        var = block_sum(q, sh) / (float)n;
+    }
+    const float scale = 1.0f / sqrtf(var + eps);
+#pragma unroll
+    for (int k = 0; k < VPT; k++) {
+        const int i = threadIdx.x + k * blockDim.x;
+        if (i < n) yr[i] = (v[k] - mean) * scale * wv[k] + rv[k];
+    }
+}
+
+template <int VPT>
+__global__ void __launch_bounds__(1024) polynorm_reg_kernel(TD x, const float *__restrict__ coef, TD dst, float eps) {
+    __shared__ float sh[32];
+    const int64_t r = blockIdx.x;
+    const float *xr = (const float *)row_ptr(x, r);
+    float *yr = (float *)row_ptr(dst, r);
+    const int n = (int)x.ne[0];
+    float z[VPT], s2 = 0.f, s4 = 0.f, s6 = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPT; k++) { const int i = threadIdx.x + k * blockDim.x; z[k] = i < n ? xr[i] : 0.f; }
+#pragma unroll
+    for (int k = 0; k < VPT; k++) { const float z2 = z[k] * z[k], z3 = z2 * z[k]; s2 += z2; s4 += z2 * z2; s6 += z3 * z3; }
+    s2 = block_sum(s2, sh); s4 = block_sum(s4, sh); s6 = block_sum(s6, sh);
+    const float inv = 1.0f / (float)n;
+    const float r1 = coef[0] / sqrtf(s2 * inv + eps), r2 = coef[1] / sqrtf(s4 * inv + eps), r3 = coef[2] / sqrtf(s6 * inv + eps), c3 = coef[3];
+#pragma unroll
+    for (int k = 0; k < VPT; k++) {
+        const int i = threadIdx.x + k * blockDim.x;
+        const float z2 = z[k] * z[k];
+        if (i < n) yr[i] = r1 * z[k] + r2 * z2 + r3 * (z2 * z[k]) + c3;
+    }
+}
+
 // ------------------------------------------------------------------------------------------------ rotation by a table
 __global__ void rope_table_kernel(TD x, const int32_t *__restrict__ pos, const float *__restrict__ freqs, TD dst, int n_dims, int neox, float mscale,
                                   int64_t total) {
@@ -140,6 +210,18 @@ extern "C" int b200_op_norm(const b200_tensor *x, const float *w, int64_t w_peri
     const int block = x->ne[0] >= 4096 ? 512 : (x->ne[0] >= 1024 ? 256 : 128);
     const cudaStream_t st = (cudaStream_t)stream;
     TD tg = gate ? td(gate) : td(x), tr = res ? td(res) : td(x);
+    if (x->ne[0] <= 16384) {  // the row fits the registers of one block
+        const int n = (int)x->ne[0];
+        const int rb = n <= 256 ? 64 : n <= 1024 ? 128 : n <= 2048 ? 256 : n <= 4096 ? 512 : 1024;
+#define B200_NORM_REG(K, G, V) norm_reg_kernel<K, G, V><<<(unsigned)rows, rb, 0, st>>>(td(x), w, w_period, tg, gate_bias, tr, res != nullptr, td(dst), eps)
+#define B200_NORM_REG_V(K, G) do { if ((n + rb - 1) / rb <= 4) B200_NORM_REG(K, G, 4); else if ((n + rb - 1) / rb <= 8) B200_NORM_REG(K, G, 8); else B200_NORM_REG(K, G, 16); } while (0)
+        if (kind == B200_NORM_RMS) { if (gate) B200_NORM_REG_V(B200_NORM_RMS, true); else B200_NORM_REG_V(B200_NORM_RMS, false); }
+        else { if (gate) B200_NORM_REG_V(B200_NORM_LAYER, true); else B200_NORM_REG_V(B200_NORM_LAYER, false); }
+#undef B200_NORM_REG_V
+#undef B200_NORM_REG
+        B200_CUDA_TRY(cudaGetLastError());
+        return B200_OK;
+    }
     const size_t smem = gate ? (size_t)x->ne[0] * 4 : 0;
 #define B200_NORM_LAUNCH(K, G)                                                                                                                   \
     do {                                                                                                                                         \
@@ -159,6 +241,16 @@ extern "C" int b200_op_polynorm(const b200_tensor *x, const float *coef, const b
                 "b200_op_polynorm: f32 rows of one shape only");
     const int64_t rows = nrows(x);
     if (rows == 0 || x->ne[0] == 0) return B200_OK;
+    if (x->ne[0] <= 16384) {
+        const int n = (int)x->ne[0];
+        const int rb = n <= 256 ? 64 : n <= 1024 ? 128 : n <= 2048 ? 256 : n <= 4096 ? 512 : 1024;
+        const int vpt = (n + rb - 1) / rb;
+        if (vpt <= 4) polynorm_reg_kernel<4><<<(unsigned)rows, rb, 0, (cudaStream_t)stream>>>(td(x), coef, td(dst), eps);
+        else if (vpt <= 8) polynorm_reg_kernel<8><<<(unsigned)rows, rb, 0, (cudaStream_t)stream>>>(td(x), coef, td(dst), eps);
+        else polynorm_reg_kernel<16><<<(unsigned)rows, rb, 0, (cudaStream_t)stream>>>(td(x), coef, td(dst), eps);
+        B200_CUDA_TRY(cudaGetLastError());
+        return B200_OK;
+    }
     const int block = x->ne[0] >= 4096 ? 512 : (x->ne[0] >= 1024 ? 256 : 128);
     polynorm_kernel<<<(unsigned)rows, block, 0, (cudaStream_t)stream>>>(td(x), coef, td(dst), eps);
     B200_CUDA_TRY(cudaGetLastError());

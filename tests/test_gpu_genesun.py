@@ -243,6 +243,30 @@ def test_dense_bf16_matmul(K, M, N):
         assert rel(got, want) < 2e-6
 
 
+@pytest.mark.parametrize("K,M,N,B", [(64, 40, 9, 3), (128, 256, 70, 5), (192, 130, 300, 2)])
+def test_dense_bf16_matmul_batched(K, M, N, B):
+    """One launch for B products; the activations of product b are a strided slice (rows of B * K values), as a per-head view is."""
+    rng = np.random.default_rng(K + M + N + B)
+    w = R.bf16_round(rng.standard_normal((B, M, K)))
+    x = rng.standard_normal((N, B, K)).astype(np.float32)
+    bits = (w.view(np.uint32) >> 16).astype(np.uint16)
+    dw, dx, dd = dev(bits, np.uint16), dev(x), H.DeviceBuffer(4 * B * N * M + 256)
+    ws_bytes = B * int(lib().b200_mul_mat_q_workspace_bytes(BF16, K, M, N))
+    ws = H.DeviceBuffer(ws_bytes + 16)
+    check(lib().b200_mul_mat_bf16_batched(dw.ptr, 2 * K, 2 * K * M, dx.ptr, B * K, K, dd.ptr, M, N * M, K, M, N, B, ws.ptr, ws_bytes, None))
+    got = dd.to_numpy(np.float32, (B, N, M))
+    want = np.einsum("nbk,bmk->bnm", R.bf16_round(x).astype(np.float64), w.astype(np.float64))
+    assert rel(got, want) < 2e-6
+    # the same batch with 1..8 columns goes through the GEMV, one grid row per product
+    n8 = min(N, 5)
+    tw, tx, td = Tensor.contiguous(dw.ptr, BF16, (K, M, B)), Tensor.contiguous(dx.ptr, F32, (K, n8, B)), Tensor.contiguous(dd.ptr, F32, (M, n8, B))
+    tx.nb[1], tx.nb[2] = 4 * B * K, 4 * K
+    check(lib().b200_op_mul_mat_float(C.byref(tw), C.byref(tx), C.byref(td), None))
+    got = dd.to_numpy(np.float32, (B, n8, M))
+    want = np.einsum("nbk,bmk->bnm", x[:n8].astype(np.float64), w.astype(np.float64))
+    assert rel(got, want) < 2e-6
+
+
 # ------------------------------------------------------------------------------------------------ whole models
 from koboldcpp_b200 import genesun as G  # noqa: E402
 from koboldcpp_b200.engine import Engine, Request  # noqa: E402
