@@ -122,6 +122,82 @@ __global__ void __launch_bounds__(WARPS * 32) latent_attn_kernel(const b200_late
     }
 }
 
+
+// Prompt batches: one CTA per (token, group of 8 heads), one warp per head.  All heads of a token see the same cells, so the CTA
+// stages a tile of LT_CELLS visible rows in shared memory once and every warp reads it from there: the cache rows cross L2 -> SM
+// once per 8 (token, head) pairs instead of once per pair, which is what bounded the kernel above on prompts.  Tiles without a
+// visible cell are skipped before anything is loaded.  Rows must be a multiple of 4 floats (16-byte copies).
+constexpr int LT_HEADS = 8, LT_CELLS = 16;
+template <int NL, int NR>
+__global__ void __launch_bounds__(LT_HEADS * 32) latent_attn_tile_kernel(const b200_latent_attn_args a) {
+    extern __shared__ float4 tile4[];  // [LT_CELLS][row floats]
+    float *tile = reinterpret_cast<float *>(tile4);
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int h = blockIdx.y * LT_HEADS + warp;
+    const bool head_ok = h < a.n_head;
+    const int KR = a.kv_rank, R = a.rot_dim, RS = KR + R, RS4 = RS / 4;
+    float q1[NL], q2[NR], acc[NL];
+    {
+        const float *ql = a.q_lat + (int64_t)(head_ok ? h : 0) * a.q_lat_s_head + (int64_t)t * a.q_lat_s_tok;
+        const float *qr = a.q_rot + (int64_t)(head_ok ? h : 0) * a.q_rot_s_head + (int64_t)t * a.q_rot_s_tok;
+#pragma unroll
+        for (int i = 0; i < NL; i++) { const int j = lane + 32 * i; q1[i] = j < KR ? ql[j] * a.scale : 0.f; acc[i] = 0.f; }
+#pragma unroll
+        for (int i = 0; i < NR; i++) { const int j = lane + 32 * i; q2[i] = j < R ? qr[j] * a.scale : 0.f; }
+    }
+    const int seq = a.tok_seq[t], pos = a.tok_pos[t];
+    const int lo = a.window > 0 ? pos - a.window : INT_MIN;
+    float m = -INFINITY, l = 0.f;
+    for (int c0 = 0; c0 < a.n_kv; c0 += LT_CELLS) {
+        bool vis = false;
+        if (lane < LT_CELLS && c0 + lane < a.n_kv) {
+            const int cp = a.cell_pos[c0 + lane];
+            vis = a.cell_seq[c0 + lane] == seq && cp <= pos && cp > lo;
+        }
+        const unsigned mask = __ballot_sync(0xffffffffu, vis);  // the same in every warp
+        if (!mask) continue;
+        __syncthreads();  // the previous tile has been read
+        for (int idx = threadIdx.x; idx < LT_CELLS * RS4; idx += LT_HEADS * 32) {
+            const int u = idx / RS4, j = idx - u * RS4;
+            if ((mask >> u) & 1u) tile4[idx] = reinterpret_cast<const float4 *>(a.cache + (int64_t)(c0 + u) * a.cache_stride)[j];
+        }
+        __syncthreads();
+        for (unsigned rest = mask; rest; rest &= rest - 1) {
+            const float *row = tile + (__ffs(rest) - 1) * RS;
+            float rv[NL], s = 0.f;
+#pragma unroll
+            for (int i = 0; i < NL; i++) { const int j = lane + 32 * i; rv[i] = j < KR ? row[j] : 0.f; s += q1[i] * rv[i]; }
+#pragma unroll
+            for (int i = 0; i < NR; i++) { const int j = lane + 32 * i; s += q2[i] * (j < R ? row[KR + j] : 0.f); }
+            s = warp_sum(s);
+            const float mn = fmaxf(m, s);
+            const float corr = expf(m - mn), p = expf(s - mn);
+            l = l * corr + p;
+#pragma unroll
+            for (int i = 0; i < NL; i++) acc[i] = acc[i] * corr + p * rv[i];
+            m = mn;
+        }
+    }
+    if (!head_ok) return;
+    const float sink = a.sink ? a.sink[h] : -INFINITY;
+    const float M = fmaxf(m, sink);
+    const float f = m == -INFINITY ? 0.f : expf(m - M);
+    const float inv = 1.0f / (l * f + (a.sink ? expf(sink - M) : 0.f));
+    float *out = a.dst + (int64_t)h * a.dst_s_head + (int64_t)t * a.dst_s_tok;
+#pragma unroll
+    for (int i = 0; i < NL; i++) { const int j = lane + 32 * i; if (j < KR) out[j] = acc[i] * f * inv; }
+}
+
+template <int NL, int NR>
+static int launch_latent_attn_tile(const b200_latent_attn_args *a, cudaStream_t st) {
+    const dim3 grid((unsigned)a->n_tokens, (unsigned)((a->n_head + LT_HEADS - 1) / LT_HEADS));
+    const size_t smem = (size_t)LT_CELLS * (a->kv_rank + a->rot_dim) * 4;
+    if (smem > 48 * 1024) B200_CUDA_TRY(cudaFuncSetAttribute(latent_attn_tile_kernel<NL, NR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    latent_attn_tile_kernel<NL, NR><<<grid, LT_HEADS * 32, smem, st>>>(*a);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
+
 template <int NL, int NR, int WARPS>
 static int launch_latent_attn3(const b200_latent_attn_args *a, cudaStream_t st) {
     const dim3 grid((unsigned)a->n_tokens, (unsigned)a->n_head);
@@ -135,6 +211,10 @@ template <int NL, int NR>
 static int launch_latent_attn2(const b200_latent_attn_args *a, cudaStream_t st) {
     // few (token, head) pairs: 16 warps share the cells of a pair
     if ((int64_t)a->n_tokens * a->n_head < 2 * 148 && a->n_kv > 64) return launch_latent_attn3<NL, NR, 16>(a, st);
+    // prompt batches: heads of a token share the staged rows (16-byte copies: rows and the cache base must allow them)
+    if (a->n_head >= 2 && (a->kv_rank + a->rot_dim) % 4 == 0 && a->cache_stride % 4 == 0 && ((uintptr_t)a->cache & 15) == 0 &&
+        (size_t)LT_CELLS * (a->kv_rank + a->rot_dim) * 4 <= 160 * 1024)
+        return launch_latent_attn_tile<NL, NR>(a, st);
     return launch_latent_attn3<NL, NR, 4>(a, st);
 }
 template <int NL>

@@ -3,23 +3,29 @@
 // Per (sequence, head) the state is a dim x vdim matrix S, a dim vector n and a running maximum m, all f32 and carried from
 // token to token in a slot of the state pool.  The columns of S never interact: a CTA owns 32 columns of one (sequence, head),
 // a warp 4 of them, a lane the rows d = lane, lane + 32, ... -- the state stays in registers for the whole token loop, the
-// per-token inputs (q, k, v, two gate values) are prefetched one token ahead, and a token costs one warp reduction per column.
+// per-token inputs come through shared memory a chunk of tokens at a time, and a token costs one warp reduction per column.
 // n . q and m are recomputed by every warp (dim MACs) instead of being exchanged.
 #include "ops_util.cuh"
 
 namespace b200 {
 using namespace opx;
 
-constexpr int ML_CW = 4, ML_WARPS = 8, ML_COLS = ML_CW * ML_WARPS;
+constexpr int ML_CW = 4, ML_WARPS = 8, ML_COLS = ML_CW * ML_WARPS, ML_CHUNK = 16, ML_THREADS = ML_WARPS * 32;
 
+// The inputs of ML_CHUNK tokens (q, k of the head, v of the CTA's 32 columns, the two gate values) are fetched by all threads
+// at once into registers while the previous chunk is being processed, then parked in shared memory, with the gate
+// non-linearities (tanh cap, log-sigmoid) already applied by one thread per token: the serial token loop reads shared memory
+// only and pays two exponentials per token, and a chunk costs one round trip to L2 that overlaps the chunk before it.
 template <int DPL>
-__global__ void __launch_bounds__(ML_WARPS * 32) mlstm_scan_kernel(const b200_mlstm_args a) {
+__global__ void __launch_bounds__(ML_THREADS) mlstm_scan_kernel(const b200_mlstm_args a) {
+    extern __shared__ float sm_[];
     const int h = blockIdx.y, s = blockIdx.z;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
     const int H = a.heads, D = a.dim, V = a.vdim;
     const int first = a.seq_info[s], count = a.seq_info[a.n_seq + s], slot = a.seq_info[2 * a.n_seq + s], fresh = a.seq_info[3 * a.n_seq + s];
-    const int col0 = blockIdx.x * ML_COLS + warp * ML_CW;
+    const int cb = blockIdx.x * ML_COLS, col0 = cb + warp * ML_CW;
     const bool active = col0 < V && count > 0;
+    float *sq = sm_, *sk = sq + ML_CHUNK * D, *sv = sk + ML_CHUNK * D, *sli = sv + ML_CHUNK * ML_COLS, *slf = sli + ML_CHUNK;
     float S[ML_CW][DPL], nn[DPL], m = 0.f;
     // n and m are kept once per CTA (column tile): a CTA never reads state that another CTA of the same launch writes
     const int nvt = gridDim.x;
@@ -36,59 +42,77 @@ __global__ void __launch_bounds__(ML_WARPS * 32) mlstm_scan_kernel(const b200_ml
         for (int c = 0; c < ML_CW; c++) S[c][i] = ok && col0 + c < V ? Sp[(int64_t)c * D + d] : 0.f;
     }
     if (active && !fresh) m = *mp;
-    __syncthreads();  // warp 0 rewrites n and m at the end: every warp has read them by now
-    if (!active) return;
     const float cap = a.gate_cap, inv_cap = 1.0f / a.gate_cap, ib = a.i_bias ? a.i_bias[h] : 0.f, fb = a.f_bias ? a.f_bias[h] : 0.f;
-    float q[DPL], k[DPL], v[ML_CW], gi, gf;
-    auto load = [&](int tok) {
-        const float *qp = a.q + (int64_t)tok * a.q_stride + (int64_t)h * D, *kp = a.k + (int64_t)tok * a.k_stride + (int64_t)h * D;
-        const float *vp = a.v + (int64_t)tok * a.v_stride + (int64_t)h * V + col0;
+    // per thread and chunk: NQK values of q and of k, 2 of v, one token's gates (threads < ML_CHUNK)
+    constexpr int NQK = (ML_CHUNK * 32 * DPL + ML_THREADS - 1) / ML_THREADS, NV = ML_CHUNK * ML_COLS / ML_THREADS;
+    float pq[NQK], pk[NQK], pv[NV], pgi = 0.f, pgf = 0.f;
+    auto fetch = [&](int t0) {
+        const int nt = min(ML_CHUNK, count - t0);
 #pragma unroll
-        for (int i = 0; i < DPL; i++) { const int d = lane + 32 * i; q[i] = d < D ? qp[d] * a.q_scale : 0.f; k[i] = d < D ? kp[d] : 0.f; }
-#pragma unroll
-        for (int c = 0; c < ML_CW; c++) v[c] = col0 + c < V ? vp[c] : 0.f;
-        gi = a.ig[(int64_t)tok * a.g_stride + h];
-        gf = a.fg[(int64_t)tok * a.g_stride + h];
-    };
-    load(first);
-    for (int t = 0; t < count; t++) {
-        const int tok = first + t;
-        float cq[DPL], ck[DPL], cv[ML_CW];
-        const float ci = gi, cf = gf;
-#pragma unroll
-        for (int i = 0; i < DPL; i++) { cq[i] = q[i]; ck[i] = k[i]; }
-#pragma unroll
-        for (int c = 0; c < ML_CW; c++) cv[c] = v[c];
-        if (t + 1 < count) load(tok + 1);
-        const float li = cap * tanhf((ci + ib) * inv_cap);
-        const float x = cap * tanhf((cf + fb) * inv_cap);
-        const float lf = fminf(x, 0.f) - log1pf(expf(-fabsf(x)));  // log sigmoid(x)
-        const float mn = fmaxf(lf + m, li);
-        const float fa = expf(lf + m - mn), fi = expf(li - mn);
-        float dn = 0.f, num[ML_CW];
-#pragma unroll
-        for (int c = 0; c < ML_CW; c++) num[c] = 0.f;
-#pragma unroll
-        for (int i = 0; i < DPL; i++) {
-            const float bk = fi * ck[i];
-            nn[i] = fa * nn[i] + bk;
-            dn += nn[i] * cq[i];
-#pragma unroll
-            for (int c = 0; c < ML_CW; c++) {
-                S[c][i] = fa * S[c][i] + bk * cv[c];
-                num[c] += S[c][i] * cq[i];
-            }
+        for (int j = 0; j < NQK; j++) {
+            const int idx = tid + j * ML_THREADS, tk = idx / D, d = idx - tk * D;
+            const bool ok = tk < nt;
+            const int64_t tok = first + t0 + tk;
+            pq[j] = ok ? a.q[tok * a.q_stride + (int64_t)h * D + d] * a.q_scale : 0.f;
+            pk[j] = ok ? a.k[tok * a.k_stride + (int64_t)h * D + d] : 0.f;
         }
-        dn = warp_sum(dn);
 #pragma unroll
-        for (int c = 0; c < ML_CW; c++) num[c] = warp_sum(num[c]);
-        const float den = fmaxf(fabsf(dn), expf(-mn)) + 1e-6f;
-        m = mn;
-        float o = num[0];
+        for (int j = 0; j < NV; j++) {
+            const int idx = tid + j * ML_THREADS, tk = idx / ML_COLS, c = idx - tk * ML_COLS;
+            pv[j] = (tk < nt && cb + c < V) ? a.v[(int64_t)(first + t0 + tk) * a.v_stride + (int64_t)h * V + cb + c] : 0.f;
+        }
+        if (tid < nt) { pgi = a.ig[(int64_t)(first + t0 + tid) * a.g_stride + h]; pgf = a.fg[(int64_t)(first + t0 + tid) * a.g_stride + h]; }
+    };
+    auto park = [&]() {
 #pragma unroll
-        for (int c = 1; c < ML_CW; c++) if (lane == c) o = num[c];
-        if (lane < ML_CW && col0 + lane < V) a.dst[(int64_t)tok * a.dst_stride + (int64_t)h * V + col0 + lane] = o / den;
+        for (int j = 0; j < NQK; j++) { const int idx = tid + j * ML_THREADS; if (idx < ML_CHUNK * D) { sq[idx] = pq[j]; sk[idx] = pk[j]; } }
+#pragma unroll
+        for (int j = 0; j < NV; j++) sv[tid + j * ML_THREADS] = pv[j];
+        if (tid < ML_CHUNK) {
+            sli[tid] = cap * tanhf((pgi + ib) * inv_cap);
+            const float x = cap * tanhf((pgf + fb) * inv_cap);
+            slf[tid] = fminf(x, 0.f) - log1pf(expf(-fabsf(x)));  // log sigmoid(x)
+        }
+    };
+    if (count > 0) fetch(0);
+    for (int t0 = 0; t0 < count; t0 += ML_CHUNK) {
+        __syncthreads();  // the previous chunk has been read
+        park();
+        __syncthreads();
+        if (t0 + ML_CHUNK < count) fetch(t0 + ML_CHUNK);  // in flight while this chunk is processed
+        if (!active) continue;
+        const int nt = min(ML_CHUNK, count - t0);
+        for (int t = 0; t < nt; t++) {
+            const float li = sli[t], lf = slf[t];
+            const float mn = fmaxf(lf + m, li);
+            const float fa = expf(lf + m - mn), fi = expf(li - mn);
+            float cv[ML_CW], dn = 0.f, num[ML_CW];
+#pragma unroll
+            for (int c = 0; c < ML_CW; c++) { cv[c] = sv[t * ML_COLS + warp * ML_CW + c]; num[c] = 0.f; }
+#pragma unroll
+            for (int i = 0; i < DPL; i++) {
+                const int d = lane + 32 * i;
+                const float cq = d < D ? sq[t * D + d] : 0.f, bk = d < D ? fi * sk[t * D + d] : 0.f;
+                nn[i] = fa * nn[i] + bk;
+                dn += nn[i] * cq;
+#pragma unroll
+                for (int c = 0; c < ML_CW; c++) {
+                    S[c][i] = fa * S[c][i] + bk * cv[c];
+                    num[c] += S[c][i] * cq;
+                }
+            }
+            dn = warp_sum(dn);
+#pragma unroll
+            for (int c = 0; c < ML_CW; c++) num[c] = warp_sum(num[c]);
+            const float den = fmaxf(fabsf(dn), expf(-mn)) + 1e-6f;
+            m = mn;
+            float o = num[0];
+#pragma unroll
+            for (int c = 1; c < ML_CW; c++) if (lane == c) o = num[c];
+            if (lane < ML_CW && col0 + lane < V) a.dst[(int64_t)(first + t0 + t) * a.dst_stride + (int64_t)h * V + col0 + lane] = o / den;
+        }
     }
+    if (!active) return;
 #pragma unroll
     for (int i = 0; i < DPL; i++) {
         const int d = lane + 32 * i;
@@ -118,11 +142,18 @@ extern "C" int b200_op_mlstm_scan(const b200_mlstm_args *a, b200_stream_t stream
     const dim3 grid((unsigned)((a->vdim + ML_COLS - 1) / ML_COLS), (unsigned)a->heads, (unsigned)a->n_seq);
     const cudaStream_t st = (cudaStream_t)stream;
     const int dpl = (a->dim + 31) / 32;
-    if (dpl <= 1) mlstm_scan_kernel<1><<<grid, ML_WARPS * 32, 0, st>>>(*a);
-    else if (dpl <= 2) mlstm_scan_kernel<2><<<grid, ML_WARPS * 32, 0, st>>>(*a);
-    else if (dpl <= 4) mlstm_scan_kernel<4><<<grid, ML_WARPS * 32, 0, st>>>(*a);
-    else if (dpl <= 8) mlstm_scan_kernel<8><<<grid, ML_WARPS * 32, 0, st>>>(*a);
-    else mlstm_scan_kernel<16><<<grid, ML_WARPS * 32, 0, st>>>(*a);
+    const size_t smem = ((size_t)2 * ML_CHUNK * a->dim + ML_CHUNK * ML_COLS + 2 * ML_CHUNK) * 4;
+#define B200_ML_LAUNCH(N)                                                                                                                     \
+    do {                                                                                                                                      \
+        if (smem > 48 * 1024) B200_CUDA_TRY(cudaFuncSetAttribute(mlstm_scan_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        mlstm_scan_kernel<N><<<grid, ML_THREADS, smem, st>>>(*a);                                                                            \
+    } while (0)
+    if (dpl <= 1) B200_ML_LAUNCH(1);
+    else if (dpl <= 2) B200_ML_LAUNCH(2);
+    else if (dpl <= 4) B200_ML_LAUNCH(4);
+    else if (dpl <= 8) B200_ML_LAUNCH(8);
+    else B200_ML_LAUNCH(16);
+#undef B200_ML_LAUNCH
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
 }

@@ -136,6 +136,34 @@ def test_latent_attn_scattered_cells_two_sequences(KR, Rr, Hh, window):
         assert rel(got[i], want) < 1e-5, (i, s, p)
 
 
+@pytest.mark.parametrize("KR,Rr,Hh,T", [(64, 16, 3, 150), (40, 4, 9, 40), (64, 8, 1, 300), (30, 3, 2, 160)])
+def test_latent_attn_prompt_batches(KR, Rr, Hh, T):
+    """Many (token, head) pairs: the kernels for prompt batches (heads of a token share staged rows; one head, or rows that are
+    not a multiple of 4 floats, take the plain kernel).  Two sequences interleaved in the cell table, every token a query."""
+    rng = np.random.default_rng(KR * 7 + Hh)
+    n_a = T - T // 3
+    n_b = T - n_a
+    n_cells = T + 11
+    rows = rng.standard_normal((n_cells, KR + Rr))
+    perm = rng.permutation(n_cells)
+    cell_seq, cell_pos = np.full(n_cells, -1), np.full(n_cells, -1)
+    cell_seq[perm[:n_a]], cell_pos[perm[:n_a]] = 1, np.arange(n_a)
+    cell_seq[perm[n_a:T]], cell_pos[perm[n_a:T]] = 0, np.arange(n_b)
+    toks = [(1, p) for p in range(n_a)] + [(0, p) for p in range(n_b)]
+    q_lat, q_rot = rng.standard_normal((T, Hh, KR)), rng.standard_normal((T, Hh, Rr))
+    sink = rng.standard_normal(Hh)
+    scale = 0.5 / math.sqrt(KR)
+    got = run_latent_attn(q_lat, q_rot, rows, cell_seq, cell_pos, [s for s, _ in toks], [p for _, p in toks], sink, scale)
+    at = 0
+    for sq, n in ((1, n_a), (0, n_b)):
+        seq_rows = np.stack([rows[np.where((cell_seq == sq) & (cell_pos == j))[0][0]] for j in range(n)])
+        k = np.repeat(seq_rows[:, None, :], Hh, 1)
+        q = np.concatenate([q_lat[at:at + n], q_rot[at:at + n]], -1)
+        want = R.sink_softmax_attention(q, k, k[..., :KR], scale, sink)
+        assert rel(got[at:at + n], want) < 1e-5, sq
+        at += n
+
+
 def test_latent_attn_far_key_and_sink_show():
     """One key far back is made to dominate; with the sink left out, or the key masked, the result would move by far more."""
     rng = np.random.default_rng(11)
