@@ -154,7 +154,9 @@ B200_API int b200_op_latent_kv_store(const float *dkv, int64_t dkv_stride, const
 /* Attention of H query heads over the latent cache (every head reads the same rows: the key is the whole row, the value its
  * first kv_rank entries).  score = scale * (q_lat . row[:kv_rank] + q_rot . row[kv_rank:]); a token sees the cells of its own
  * sequence with cell_pos <= tok_pos (and cell_pos > tok_pos - window when window > 0); softmax in f32 whose denominator also
- * holds exp(sink[h]) when sink != NULL.  Strides are in floats.  dst[h][t][:kv_rank] = sum_c p_c row_c[:kv_rank]. */
+ * holds exp(sink[h]) when sink != NULL.  Strides are in floats.  dst[h][t][:kv_rank] = sum_c p_c row_c[:kv_rank].
+ * bf16_products != 0 allows the two contractions of a prompt batch (16 tokens or more) to take queries, rows and weights rounded
+ * to bf16 with f32 accumulation (scores, maxima, exponentials and sums stay f32); 0 keeps every product in f32. */
 typedef struct {
     const float *q_lat; int64_t q_lat_s_head, q_lat_s_tok;
     const float *q_rot; int64_t q_rot_s_head, q_rot_s_tok;
@@ -164,6 +166,7 @@ typedef struct {
     float *dst; int64_t dst_s_head, dst_s_tok;
     int32_t kv_rank, rot_dim, n_head, n_tokens, n_kv, window;
     float scale;
+    int32_t bf16_products;
 } b200_latent_attn_args;
 B200_API int b200_op_latent_attn(const b200_latent_attn_args *a, b200_stream_t stream);
 

@@ -124,6 +124,7 @@ static void run_ext(ExecCtx &x, const ggml_tensor *n) {
             a.dst = (float *)n->data; a.dst_s_tok = (int64_t)(n->nb[1] / 4); a.dst_s_head = (int64_t)(n->nb[2] / 4);
             a.kv_rank = n->op_params[2]; a.rot_dim = (int32_t)s[2]->ne[0] - a.kv_rank; a.n_head = (int32_t)s[0]->ne[1]; a.n_tokens = (int32_t)s[0]->ne[2];
             a.n_kv = (int32_t)s[6]->ne[0]; a.window = n->op_params[4]; a.scale = ext_f(n, 3);
+            a.bf16_products = n->op_params[5];
             B200_CHECK_RC(b200_op_latent_attn(&a, x.stream));
             break;
         }

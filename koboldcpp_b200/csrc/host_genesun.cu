@@ -312,6 +312,7 @@ int gs_build(b200_llama *m, const BatchShape &bs) {
             ggml_tensor *o_lat = b.alloc_result(GGML_TYPE_F32, KR, T, H);
             b.ext(o_lat, B200_EXT_LATENT_ATTN, {q_lat, q_rot, L.store_node, L.sink, tok_seq, pos, cell_seq, cell_pos});
             o_lat->op_params[2] = (int32_t)KR; Builder::set_f(o_lat, 3, lp.scale); o_lat->op_params[4] = lp.window;
+            o_lat->op_params[5] = L.uk_t->type == GGML_TYPE_BF16;  // bf16 weights: the attention products of a prompt batch may be bf16 as well
             ggml_tensor *uv3 = b.view_3d(L.uv, KR, V, H, L.uv->nb[1], L.uv->nb[1] * (size_t)V, 0);
             ggml_tensor *o = b.permute(b.mul_mat(uv3, o_lat), 0, 2, 1, 3);                        // [V, T, H] seen as [V, H, T]
             ggml_tensor *gate = b.view_3d(P, V, H, T, (size_t)V * 4, P->nb[1], (size_t)part_offset(parts, np, "mix.g", nullptr) * 4);

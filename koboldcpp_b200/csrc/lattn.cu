@@ -6,6 +6,7 @@
 // streamed once per (token, head group) and never expanded to per-head keys and values in HBM.
 // Visibility is decided per (token, cell) from (sequence, position) pairs: no mask tensor is built, uploaded or read.
 #include "ops_util.cuh"
+#include <cuda_bf16.h>
 
 namespace b200 {
 using namespace opx;
@@ -198,6 +199,219 @@ static int launch_latent_attn_tile(const b200_latent_attn_args *a, cudaStream_t 
     return B200_OK;
 }
 
+// Prompt batches with bf16 products: the tensor cores take both contractions (mma.sync.m16n8k16, bf16 in, f32 accumulators).
+// One CTA per (16 consecutive tokens of the batch, head).  Its query rows [q_lat | q_rot] sit in shared memory as bf16; the cache
+// rows come through in tiles of 16 cells, converted to bf16 on the way in.  The LM_WARPS warps split the long contraction of the
+// scores (kv_rank + rot_dim values) by 16-wide steps and add their partial 16 x 16 score tiles through shared memory, so every
+// warp then holds the whole tile in accumulator layout; scale, visibility, the running maximum and the exponentials are f32 and
+// the same in every warp.  For the second product each warp owns a share of the kv_rank output columns (16-wide column groups
+// w, w + LM_WARPS, ...), NJ groups per warp, which keeps the f32 accumulators of a 16 x kv_rank result within the register file.
+// A tile none of whose cells is visible to any of the 16 tokens is skipped before it is loaded; rows of free cells are read as zeros
+// (their weight is zero, and zero times whatever an unwritten row holds must not reach the sum).
+constexpr int LM_TOK = 16, LM_CELLS = 16, LM_WARPS = 4;
+__device__ __forceinline__ void lm_ldsm4(unsigned addr, unsigned &r0, unsigned &r1, unsigned &r2, unsigned &r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void lm_ldsm4_t(unsigned addr, unsigned &r0, unsigned &r1, unsigned &r2, unsigned &r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void lm_mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned lm_pack_bf2(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const unsigned *>(&v);
+}
+
+template <int NJ>
+__global__ void __launch_bounds__(LM_WARPS * 32) latent_attn_mma_kernel(const b200_latent_attn_args a) {
+    extern __shared__ float4 lm_smem4[];
+    const int KR = a.kv_rank, RS = KR + a.rot_dim, RS16 = (RS + 15) & ~15, NK = RS16 / 16, NJG = KR / 16;
+    const int stride = RS16 * 2 + 16;  // bytes per bf16 row: 8 consecutive rows start in 8 different 16-byte bank groups (ldmatrix)
+    unsigned char *qs = reinterpret_cast<unsigned char *>(lm_smem4);  // [LM_TOK][stride]
+    unsigned char *ts = qs + LM_TOK * stride;                         // [LM_CELLS][stride]
+    float *sp = reinterpret_cast<float *>(ts + LM_CELLS * stride);    // [LM_WARPS][32 lanes][8]: partial score tiles in accumulator layout
+    int *tseq = reinterpret_cast<int *>(sp + LM_WARPS * 256), *tpos = tseq + LM_TOK, *tlo = tpos + LM_TOK, *cseq = tlo + LM_TOK, *cpos = cseq + LM_CELLS;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+    const int t0 = blockIdx.x * LM_TOK, h = blockIdx.y;
+
+    if (tid < LM_TOK) {
+        const int t = t0 + tid;
+        const bool ok = t < a.n_tokens;
+        const int p = ok ? a.tok_pos[t] : 0;
+        tseq[tid] = ok ? a.tok_seq[t] : -2;  // matches no cell
+        tpos[tid] = p;
+        tlo[tid] = a.window > 0 ? p - a.window : INT_MIN;
+    }
+    for (int idx = tid; idx < LM_TOK * RS16; idx += LM_WARPS * 32) {
+        const int i = idx / RS16, j = idx - i * RS16, t = t0 + i;
+        float v = 0.f;
+        if (t < a.n_tokens) {
+            if (j < KR) v = a.q_lat[(int64_t)h * a.q_lat_s_head + (int64_t)t * a.q_lat_s_tok + j];
+            else if (j < RS) v = a.q_rot[(int64_t)h * a.q_rot_s_head + (int64_t)t * a.q_rot_s_tok + (j - KR)];
+        }
+        *reinterpret_cast<__nv_bfloat16 *>(qs + i * stride + j * 2) = __float2bfloat16_rn(v);
+    }
+    __syncthreads();
+    int rs[2], rp[2], rl[2];
+#pragma unroll
+    for (int hh = 0; hh < 2; hh++) { rs[hh] = tseq[g + 8 * hh]; rp[hh] = tpos[g + 8 * hh]; rl[hh] = tlo[g + 8 * hh]; }
+
+    // ldmatrix lane addresses: matrix mi = lane >> 3, row mr = lane & 7
+    const int mi = lane >> 3, mr = lane & 7;
+    const unsigned qs_u = (unsigned)__cvta_generic_to_shared(qs), ts_u = (unsigned)__cvta_generic_to_shared(ts);
+    const unsigned a_off = (unsigned)(((mi & 1) * 8 + mr) * stride + (mi >> 1) * 16);  // A (queries) and transposed B (values): rows (mi&1)*8.., columns (mi>>1)*8..
+    const unsigned k_off = (unsigned)(((mi >> 1) * 8 + mr) * stride + (mi & 1) * 16);  // B (keys): cells (mi>>1)*8.., values (mi&1)*8..
+
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};  // l: this lane's share (its 4 cells of every tile)
+    float o[NJ][2][4];
+#pragma unroll
+    for (int jj = 0; jj < NJ; jj++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) o[jj][0][e] = o[jj][1][e] = 0.f;
+    const int RS4 = RS / 4, RS16_4 = RS16 / 4;
+
+    for (int c0 = 0; c0 < a.n_kv; c0 += LM_CELLS) {
+        bool any = false;
+        for (int idx = tid; idx < LM_TOK * LM_CELLS; idx += LM_WARPS * 32) {
+            const int i = idx >> 4, c = c0 + (idx & 15);
+            if (c < a.n_kv) {
+                const int cp = a.cell_pos[c];
+                any |= a.cell_seq[c] == tseq[i] && cp <= tpos[i] && cp > tlo[i];
+            }
+        }
+        if (!__syncthreads_or(any)) continue;  // also: the previous tile, its scores and its cell table have been read
+        if (tid < LM_CELLS) {
+            const int c = c0 + tid;
+            cseq[tid] = c < a.n_kv ? a.cell_seq[c] : -1;
+            cpos[tid] = c < a.n_kv ? a.cell_pos[c] : -1;
+        }
+        for (int idx = tid; idx < LM_CELLS * RS16_4; idx += LM_WARPS * 32) {
+            const int u = idx / RS16_4, j = idx - u * RS16_4, c = c0 + u;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (j < RS4 && c < a.n_kv && a.cell_seq[c] >= 0) v = reinterpret_cast<const float4 *>(a.cache + (int64_t)c * a.cache_stride)[j];
+            *reinterpret_cast<uint2 *>(ts + u * stride + j * 8) = make_uint2(lm_pack_bf2(v.x, v.y), lm_pack_bf2(v.z, v.w));
+        }
+        __syncthreads();
+        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        for (int ks = warp; ks < NK; ks += LM_WARPS) {
+            unsigned qa[4], b0, b1, b2, b3;
+            lm_ldsm4(qs_u + a_off + ks * 32, qa[0], qa[1], qa[2], qa[3]);
+            lm_ldsm4(ts_u + k_off + ks * 32, b0, b1, b2, b3);
+            lm_mma_bf16(s[0], qa, b0, b1);  // cells 0-7
+            lm_mma_bf16(s[1], qa, b2, b3);  // cells 8-15
+        }
+        {
+            float4 *mine = reinterpret_cast<float4 *>(sp + (warp * 32 + lane) * 8);
+            mine[0] = make_float4(s[0][0], s[0][1], s[0][2], s[0][3]);
+            mine[1] = make_float4(s[1][0], s[1][1], s[1][2], s[1][3]);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int e = 0; e < 4; e++) s[0][e] = s[1][e] = 0.f;
+#pragma unroll
+        for (int w = 0; w < LM_WARPS; w++) {  // the same order in every warp: all hold the same sums
+            const float4 *part = reinterpret_cast<const float4 *>(sp + (w * 32 + lane) * 8);
+            const float4 p0 = part[0], p1 = part[1];
+            s[0][0] += p0.x; s[0][1] += p0.y; s[0][2] += p0.z; s[0][3] += p0.w;
+            s[1][0] += p1.x; s[1][1] += p1.y; s[1][2] += p1.z; s[1][3] += p1.w;
+        }
+        // s[nb][2 hh + e]: token row g + 8 hh, cell 8 nb + 2 t4 + e
+        unsigned pa[4];
+        float alpha[2];
+#pragma unroll
+        for (int hh = 0; hh < 2; hh++) {
+#pragma unroll
+            for (int nb = 0; nb < 2; nb++)
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    const int u = 8 * nb + 2 * t4 + e, cp = cpos[u];
+                    const bool vis = cseq[u] == rs[hh] && cp <= rp[hh] && cp > rl[hh];
+                    s[nb][2 * hh + e] = vis ? s[nb][2 * hh + e] * a.scale : -INFINITY;
+                }
+            float mx = fmaxf(fmaxf(s[0][2 * hh], s[0][2 * hh + 1]), fmaxf(s[1][2 * hh], s[1][2 * hh + 1]));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float mn = fmaxf(m[hh], mx);
+            const bool none = mn == -INFINITY;  // nothing seen so far by this row
+            alpha[hh] = none ? 1.0f : expf(m[hh] - mn);
+            const float p0 = none ? 0.f : expf(s[0][2 * hh] - mn), p1 = none ? 0.f : expf(s[0][2 * hh + 1] - mn);
+            const float p2 = none ? 0.f : expf(s[1][2 * hh] - mn), p3 = none ? 0.f : expf(s[1][2 * hh + 1] - mn);
+            l[hh] = l[hh] * alpha[hh] + ((p0 + p1) + (p2 + p3));
+            m[hh] = mn;
+            pa[hh] = lm_pack_bf2(p0, p1);      // a0 / a1: row g (+8), cells 2 t4, 2 t4 + 1
+            pa[2 + hh] = lm_pack_bf2(p2, p3);  // a2 / a3: cells 8 + 2 t4, ...
+        }
+        const bool rescale = __any_sync(0xffffffffu, alpha[0] != 1.0f || alpha[1] != 1.0f);
+#pragma unroll
+        for (int jj = 0; jj < NJ; jj++) {
+            const int j = warp + jj * LM_WARPS;
+            if (j >= NJG) break;
+            if (rescale) {
+#pragma unroll
+                for (int half = 0; half < 2; half++) { o[jj][half][0] *= alpha[0]; o[jj][half][1] *= alpha[0]; o[jj][half][2] *= alpha[1]; o[jj][half][3] *= alpha[1]; }
+            }
+            unsigned b0, b1, b2, b3;
+            lm_ldsm4_t(ts_u + a_off + j * 32, b0, b1, b2, b3);
+            lm_mma_bf16(o[jj][0], pa, b0, b1);  // columns 16 j .. 16 j + 7
+            lm_mma_bf16(o[jj][1], pa, b2, b3);  // columns 16 j + 8 .. 16 j + 15
+        }
+    }
+    const float sink = a.sink ? a.sink[h] : -INFINITY;
+    float w[2];
+#pragma unroll
+    for (int hh = 0; hh < 2; hh++) {
+        float lt = l[hh];
+        lt += __shfl_xor_sync(0xffffffffu, lt, 1);
+        lt += __shfl_xor_sync(0xffffffffu, lt, 2);
+        const float M = fmaxf(m[hh], sink);
+        const float f = m[hh] == -INFINITY ? 0.f : expf(m[hh] - M);
+        const float den = lt * f + (a.sink ? expf(sink - M) : 0.f);
+        w[hh] = den > 0.f ? f / den : 0.f;
+    }
+#pragma unroll
+    for (int jj = 0; jj < NJ; jj++) {
+        const int j = warp + jj * LM_WARPS;
+        if (j >= NJG) break;
+#pragma unroll
+        for (int hh = 0; hh < 2; hh++) {
+            const int t = t0 + g + 8 * hh;
+            if (t >= a.n_tokens) continue;
+            float *out = a.dst + (int64_t)h * a.dst_s_head + (int64_t)t * a.dst_s_tok + 16 * j + 2 * t4;
+            out[0] = o[jj][0][2 * hh] * w[hh]; out[1] = o[jj][0][2 * hh + 1] * w[hh];
+            out[8] = o[jj][1][2 * hh] * w[hh]; out[9] = o[jj][1][2 * hh + 1] * w[hh];
+        }
+    }
+}
+
+static size_t latent_attn_mma_smem(const b200_latent_attn_args *a) {
+    const int rs16 = (a->kv_rank + a->rot_dim + 15) & ~15;
+    return (size_t)(LM_TOK + LM_CELLS) * (rs16 * 2 + 16) + (size_t)LM_WARPS * 256 * 4 + (3 * LM_TOK + 2 * LM_CELLS) * 4;
+}
+template <int NJ>
+static int launch_latent_attn_mma2(const b200_latent_attn_args *a, cudaStream_t st) {
+    const dim3 grid((unsigned)((a->n_tokens + LM_TOK - 1) / LM_TOK), (unsigned)a->n_head);
+    const size_t smem = latent_attn_mma_smem(a);
+    if (smem > 48 * 1024) B200_CUDA_TRY(cudaFuncSetAttribute(latent_attn_mma_kernel<NJ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    latent_attn_mma_kernel<NJ><<<grid, LM_WARPS * 32, smem, st>>>(*a);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
+// bf16 products were asked for, there are enough tokens to fill 16-row tiles, and the sizes fit the 16-wide fragments and 16-byte copies
+static bool latent_attn_mma_ok(const b200_latent_attn_args *a) {
+    return a->bf16_products && a->n_tokens >= LM_TOK && a->kv_rank % 16 == 0 && (a->kv_rank + a->rot_dim) % 4 == 0 && a->cache_stride % 4 == 0 &&
+           ((uintptr_t)a->cache & 15) == 0 && latent_attn_mma_smem(a) <= 200 * 1024;
+}
+static int launch_latent_attn_mma(const b200_latent_attn_args *a, cudaStream_t st) {
+    const int nj = (a->kv_rank / 16 + LM_WARPS - 1) / LM_WARPS;
+    if (nj <= 1) return launch_latent_attn_mma2<1>(a, st);
+    if (nj <= 2) return launch_latent_attn_mma2<2>(a, st);
+    if (nj <= 4) return launch_latent_attn_mma2<4>(a, st);
+    if (nj <= 8) return launch_latent_attn_mma2<8>(a, st);
+    return launch_latent_attn_mma2<16>(a, st);
+}
+
 template <int NL, int NR, int WARPS>
 static int launch_latent_attn3(const b200_latent_attn_args *a, cudaStream_t st) {
     const dim3 grid((unsigned)a->n_tokens, (unsigned)a->n_head);
@@ -249,6 +463,7 @@ extern "C" int b200_op_latent_attn(const b200_latent_attn_args *a, b200_stream_t
                 a->cache_stride >= a->kv_rank + a->rot_dim, B200_ERR_UNSUPPORTED, "b200_op_latent_attn: kv_rank <= 1024, rot_dim <= 128, heads <= 65535");
     if (a->n_tokens == 0) return B200_OK;
     const cudaStream_t st = (cudaStream_t)stream;
+    if (latent_attn_mma_ok(a)) return launch_latent_attn_mma(a, st);
     const int nl = (a->kv_rank + 31) / 32;
     if (nl <= 2) return launch_latent_attn<2>(a, st);
     if (nl <= 4) return launch_latent_attn<4>(a, st);

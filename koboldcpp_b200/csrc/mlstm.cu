@@ -3,7 +3,9 @@
 // Per (sequence, head) the state is a dim x vdim matrix S, a dim vector n and a running maximum m, all f32 and carried from
 // token to token in a slot of the state pool.  The columns of S never interact: a CTA owns 32 columns of one (sequence, head),
 // a warp 4 of them, a lane the rows d = lane, lane + 32, ... -- the state stays in registers for the whole token loop, the
-// per-token inputs come through shared memory a chunk of tokens at a time, and a token costs one warp reduction per column.
+// per-token inputs come through shared memory a chunk of tokens at a time.  The sums over the rows (n . q and one numerator per
+// column) do not feed the recurrence, so the token loop only parks each lane's share in shared memory and the warp adds them
+// up for ML_RG tokens at a time, one sum per lane, outside the serial chain.
 // n . q and m are recomputed by every warp (dim MACs) instead of being exchanged.
 #include "ops_util.cuh"
 
@@ -11,6 +13,7 @@ namespace b200 {
 using namespace opx;
 
 constexpr int ML_CW = 4, ML_WARPS = 8, ML_COLS = ML_CW * ML_WARPS, ML_CHUNK = 16, ML_THREADS = ML_WARPS * 32;
+constexpr int ML_RG = 8, ML_NP = ML_CW + 1;  // tokens whose reductions are done together; sums per token (n . q and one numerator per column)
 
 // The inputs of ML_CHUNK tokens (q, k of the head, v of the CTA's 32 columns, the two gate values) are fetched by all threads
 // at once into registers while the previous chunk is being processed, then parked in shared memory, with the gate
@@ -26,6 +29,7 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_scan_kernel(const b200_mlstm
     const int cb = blockIdx.x * ML_COLS, col0 = cb + warp * ML_CW;
     const bool active = col0 < V && count > 0;
     float *sq = sm_, *sk = sq + ML_CHUNK * D, *sv = sk + ML_CHUNK * D, *sli = sv + ML_CHUNK * ML_COLS, *slf = sli + ML_CHUNK;
+    float *wpart = slf + ML_CHUNK + warp * (ML_RG * ML_NP * 32 + ML_RG * ML_NP + ML_RG), *wred = wpart + ML_RG * ML_NP * 32, *wmn = wred + ML_RG * ML_NP;  // this warp's own
     float S[ML_CW][DPL], nn[DPL], m = 0.f;
     // n and m are kept once per CTA (column tile): a CTA never reads state that another CTA of the same launch writes
     const int nvt = gridDim.x;
@@ -82,34 +86,52 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_scan_kernel(const b200_mlstm
         if (t0 + ML_CHUNK < count) fetch(t0 + ML_CHUNK);  // in flight while this chunk is processed
         if (!active) continue;
         const int nt = min(ML_CHUNK, count - t0);
-        for (int t = 0; t < nt; t++) {
-            const float li = sli[t], lf = slf[t];
-            const float mn = fmaxf(lf + m, li);
-            const float fa = expf(lf + m - mn), fi = expf(li - mn);
-            float cv[ML_CW], dn = 0.f, num[ML_CW];
+        for (int g0 = 0; g0 < nt; g0 += ML_RG) {
+            const int ng = min(ML_RG, nt - g0);
+            for (int tg = 0; tg < ng; tg++) {
+                const int t = g0 + tg;
+                const float li = sli[t], lf = slf[t];
+                const float mn = fmaxf(lf + m, li);
+                const float fa = expf(lf + m - mn), fi = expf(li - mn);
+                float cv[ML_CW], dn = 0.f, num[ML_CW];
 #pragma unroll
-            for (int c = 0; c < ML_CW; c++) { cv[c] = sv[t * ML_COLS + warp * ML_CW + c]; num[c] = 0.f; }
+                for (int c = 0; c < ML_CW; c++) { cv[c] = sv[t * ML_COLS + warp * ML_CW + c]; num[c] = 0.f; }
 #pragma unroll
-            for (int i = 0; i < DPL; i++) {
-                const int d = lane + 32 * i;
-                const float cq = d < D ? sq[t * D + d] : 0.f, bk = d < D ? fi * sk[t * D + d] : 0.f;
-                nn[i] = fa * nn[i] + bk;
-                dn += nn[i] * cq;
+                for (int i = 0; i < DPL; i++) {
+                    const int d = lane + 32 * i;
+                    const float cq = d < D ? sq[t * D + d] : 0.f, bk = d < D ? fi * sk[t * D + d] : 0.f;
+                    nn[i] = fa * nn[i] + bk;
+                    dn += nn[i] * cq;
 #pragma unroll
-                for (int c = 0; c < ML_CW; c++) {
-                    S[c][i] = fa * S[c][i] + bk * cv[c];
-                    num[c] += S[c][i] * cq;
+                    for (int c = 0; c < ML_CW; c++) {
+                        S[c][i] = fa * S[c][i] + bk * cv[c];
+                        num[c] += S[c][i] * cq;
+                    }
                 }
+                // the lane's shares of n . q and of the ML_CW numerators wait in shared memory: nothing of the recurrence depends on them
+                float *pp = wpart + tg * ML_NP * 32;
+                pp[lane] = dn;
+#pragma unroll
+                for (int c = 0; c < ML_CW; c++) pp[(1 + c) * 32 + lane] = num[c];
+                if (lane == 0) wmn[tg] = mn;
+                m = mn;
             }
-            dn = warp_sum(dn);
+            __syncwarp();
+            // ng * ML_NP sums of 32 shares each, one sum per lane; lane L starts at share L so that the lanes hit different banks
+            for (int p = lane; p < ng * ML_NP; p += 32) {
+                const float *pp = wpart + p * 32;
+                float s0 = 0.f, s1 = 0.f;
 #pragma unroll
-            for (int c = 0; c < ML_CW; c++) num[c] = warp_sum(num[c]);
-            const float den = fmaxf(fabsf(dn), expf(-mn)) + 1e-6f;
-            m = mn;
-            float o = num[0];
-#pragma unroll
-            for (int c = 1; c < ML_CW; c++) if (lane == c) o = num[c];
-            if (lane < ML_CW && col0 + lane < V) a.dst[(int64_t)(first + t0 + t) * a.dst_stride + (int64_t)h * V + col0 + lane] = o / den;
+                for (int i = 0; i < 32; i += 2) { s0 += pp[(i + lane) & 31]; s1 += pp[(i + 1 + lane) & 31]; }
+                wred[p] = s0 + s1;
+            }
+            __syncwarp();
+            for (int idx = lane; idx < ng * ML_CW; idx += 32) {
+                const int tg = idx / ML_CW, c = idx - tg * ML_CW;
+                const float den = fmaxf(fabsf(wred[tg * ML_NP]), expf(-wmn[tg])) + 1e-6f;
+                if (col0 + c < V) a.dst[(int64_t)(first + t0 + g0 + tg) * a.dst_stride + (int64_t)h * V + col0 + c] = wred[tg * ML_NP + 1 + c] / den;
+            }
+            __syncwarp();
         }
     }
     if (!active) return;
@@ -142,7 +164,7 @@ extern "C" int b200_op_mlstm_scan(const b200_mlstm_args *a, b200_stream_t stream
     const dim3 grid((unsigned)((a->vdim + ML_COLS - 1) / ML_COLS), (unsigned)a->heads, (unsigned)a->n_seq);
     const cudaStream_t st = (cudaStream_t)stream;
     const int dpl = (a->dim + 31) / 32;
-    const size_t smem = ((size_t)2 * ML_CHUNK * a->dim + ML_CHUNK * ML_COLS + 2 * ML_CHUNK) * 4;
+    const size_t smem = ((size_t)2 * ML_CHUNK * a->dim + ML_CHUNK * ML_COLS + 2 * ML_CHUNK + (size_t)ML_WARPS * (ML_RG * ML_NP * 32 + ML_RG * ML_NP + ML_RG)) * 4;
 #define B200_ML_LAUNCH(N)                                                                                                                     \
     do {                                                                                                                                      \
         if (smem > 48 * 1024) B200_CUDA_TRY(cudaFuncSetAttribute(mlstm_scan_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \

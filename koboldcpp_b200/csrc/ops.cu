@@ -684,11 +684,72 @@ __global__ void __launch_bounds__(128) gemv_bf16_kernel(const unsigned char *__r
         }
 }
 
+// Three to eight activation rows: the activations outweigh the weights NC to 1 on the way through L1, so a warp keeps
+// GW_ROWS weight rows going against one fetch of the activation slice (NC x 32 bytes per lane), and the four warps of a CTA split
+// K among themselves so that a matrix of a few thousand rows still puts enough loads in flight; partial sums meet in shared memory.
+constexpr int GW_ROWS = 8, GW_WARPS = 4;
+template <int NC>
+__global__ void __launch_bounds__(GW_WARPS * 32) gemv_bf16_wide_kernel(const unsigned char *__restrict__ W, int64_t w_row_bytes, int64_t w_batch_bytes, const float *__restrict__ X,
+                                                                       int64_t x_stride, int64_t x_batch, float *__restrict__ dst, int64_t dst_stride, int64_t dst_batch,
+                                                                       int64_t K, int64_t M) {
+    __shared__ float part[GW_WARPS][GW_ROWS * NC];
+    const int64_t m0 = (int64_t)blockIdx.x * GW_ROWS;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    W += (int64_t)blockIdx.y * w_batch_bytes; X += (int64_t)blockIdx.y * x_batch; dst += (int64_t)blockIdx.y * dst_batch;
+    const uint4 *wr[GW_ROWS];
+#pragma unroll
+    for (int r = 0; r < GW_ROWS; r++) wr[r] = reinterpret_cast<const uint4 *>(W + (m0 + r < M ? m0 + r : m0) * w_row_bytes);
+    float acc[GW_ROWS][NC];
+#pragma unroll
+    for (int r = 0; r < GW_ROWS; r++)
+#pragma unroll
+        for (int c = 0; c < NC; c++) acc[r][c] = 0.f;
+    const int64_t nv = K / 8;
+    for (int64_t i = warp * 32 + lane; i < nv; i += GW_WARPS * 32) {
+        uint4 a[GW_ROWS];
+#pragma unroll
+        for (int r = 0; r < GW_ROWS; r++) a[r] = ld_stream16(wr[r] + i);
+#pragma unroll
+        for (int c = 0; c < NC; c++) {
+            const float4 *xa = reinterpret_cast<const float4 *>(X + c * x_stride + i * 8);
+            const float4 x0 = xa[0], x1 = xa[1];
+            const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+            for (int r = 0; r < GW_ROWS; r++) {
+                const unsigned wa[4] = {a[r].x, a[r].y, a[r].z, a[r].w};
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[r][c] += __uint_as_float(wa[j] << 16) * xs[2 * j] + __uint_as_float(wa[j] & 0xffff0000u) * xs[2 * j + 1];
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < GW_ROWS; r++)
+#pragma unroll
+        for (int c = 0; c < NC; c++) {
+            const float v = warp_sum(acc[r][c]);
+            if (lane == 0) part[warp][r * NC + c] = v;
+        }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < GW_ROWS * NC; idx += GW_WARPS * 32) {
+        const int r = idx / NC, c = idx - r * NC;
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < GW_WARPS; w++) v += part[w][idx];
+        if (m0 + r < M) dst[c * dst_stride + m0 + r] = v;
+    }
+}
+
 template <int NC>
 static void launch_gemv_bf16(const b200_tensor *w, const b200_tensor *x, const b200_tensor *dst, cudaStream_t st) {
     const int64_t M = w->ne[1], nb = x->ne[2];
     const int64_t wb = w->ne[2] > 1 ? (int64_t)w->nb[2] : 0;
-    constexpr int RPW = NC >= 3 ? 2 : 1;
+    if constexpr (NC >= 3) {
+        const dim3 grid((unsigned)((M + GW_ROWS - 1) / GW_ROWS), (unsigned)nb);
+        gemv_bf16_wide_kernel<NC><<<grid, GW_WARPS * 32, 0, st>>>((const unsigned char *)w->data, (int64_t)w->nb[1], wb, (const float *)x->data, (int64_t)(x->nb[1] / 4),
+                                                                  (int64_t)(x->nb[2] / 4), (float *)dst->data, (int64_t)(dst->nb[1] / 4), (int64_t)(dst->nb[2] / 4), w->ne[0], M);
+        return;
+    }
+    constexpr int RPW = 1;
     const dim3 grid((unsigned)((M + 4 * RPW - 1) / (4 * RPW)), (unsigned)nb);
     gemv_bf16_kernel<NC, RPW><<<grid, 128, 0, st>>>((const unsigned char *)w->data, (int64_t)w->nb[1], wb, (const float *)x->data, (int64_t)(x->nb[1] / 4),
                                                     (int64_t)(x->nb[2] / 4), (float *)dst->data, (int64_t)(dst->nb[1] / 4), (int64_t)(dst->nb[2] / 4), w->ne[0], M);

@@ -70,7 +70,7 @@ class LatentAttnArgs(C.Structure):
                 ("q_rot_s_tok", C.c_int64), ("cache", C.c_void_p), ("cache_stride", C.c_int64), ("cell_seq", C.c_void_p), ("cell_pos", C.c_void_p),
                 ("tok_seq", C.c_void_p), ("tok_pos", C.c_void_p), ("sink", C.c_void_p), ("dst", C.c_void_p), ("dst_s_head", C.c_int64), ("dst_s_tok", C.c_int64),
                 ("kv_rank", C.c_int32), ("rot_dim", C.c_int32), ("n_head", C.c_int32), ("n_tokens", C.c_int32), ("n_kv", C.c_int32), ("window", C.c_int32),
-                ("scale", C.c_float)]
+                ("scale", C.c_float), ("bf16_products", C.c_int32)]
 
 
 class MlstmArgs(C.Structure):

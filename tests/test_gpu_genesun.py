@@ -98,7 +98,7 @@ def test_weighted_sum_and_sigmoid_mul():
     assert rel(dd.to_numpy(np.float32, (3, 4, 6)), a.transpose(1, 0, 2) * R.sigmoid(b)) < 2e-6
 
 
-def run_latent_attn(q_lat, q_rot, rows, cell_seq, cell_pos, tok_seq, tok_pos, sink, scale, window=0):
+def run_latent_attn(q_lat, q_rot, rows, cell_seq, cell_pos, tok_seq, tok_pos, sink, scale, window=0, bf16=0):
     T, Hh, KR = q_lat.shape
     Rr = q_rot.shape[-1]
     bufs = [dev(q_lat), dev(q_rot), dev(rows), dev(cell_seq, np.int32), dev(cell_pos, np.int32), dev(tok_seq, np.int32), dev(tok_pos, np.int32)]
@@ -107,7 +107,7 @@ def run_latent_attn(q_lat, q_rot, rows, cell_seq, cell_pos, tok_seq, tok_pos, si
     a = LatentAttnArgs(q_lat=bufs[0].ptr, q_lat_s_head=KR, q_lat_s_tok=Hh * KR, q_rot=bufs[1].ptr, q_rot_s_head=Rr, q_rot_s_tok=Hh * Rr, cache=bufs[2].ptr,
                        cache_stride=rows.shape[1], cell_seq=bufs[3].ptr, cell_pos=bufs[4].ptr, tok_seq=bufs[5].ptr, tok_pos=bufs[6].ptr,
                        sink=dsink.ptr if dsink else None, dst=out.ptr, dst_s_head=KR, dst_s_tok=Hh * KR, kv_rank=KR, rot_dim=Rr, n_head=Hh, n_tokens=T,
-                       n_kv=len(cell_seq), window=window, scale=scale)
+                       n_kv=len(cell_seq), window=window, scale=scale, bf16_products=bf16)
     check(lib().b200_op_latent_attn(C.byref(a), None))
     return out.to_numpy(np.float32, (T, Hh, KR))
 
@@ -161,6 +161,42 @@ def test_latent_attn_prompt_batches(KR, Rr, Hh, T):
         q = np.concatenate([q_lat[at:at + n], q_rot[at:at + n]], -1)
         want = R.sink_softmax_attention(q, k, k[..., :KR], scale, sink)
         assert rel(got[at:at + n], want) < 1e-5, sq
+        at += n
+
+
+@pytest.mark.parametrize("KR,Rr,Hh,T,window", [(64, 16, 3, 150, 0), (16, 0, 2, 16, 0), (48, 4, 5, 77, 9), (128, 40, 1, 300, 0), (80, 8, 2, 33, 0), (320, 24, 2, 50, 17)])
+def test_latent_attn_prompt_batches_bf16_products(KR, Rr, Hh, T, window):
+    """16 tokens or more with bf16 products allowed: the tensor-core kernel (16-token tiles, 16-cell tiles, the last of either
+    ragged).  Inputs are bf16 values already, so what remains against the plain statement is the rounding of the weights.
+    Two sequences interleaved in a shuffled cell table; free cells hold NaN and must not reach any sum."""
+    rng = np.random.default_rng(KR * 5 + T)
+    n_a = T - T // 3
+    n_b = T - n_a
+    n_cells = T + 13
+    rows = R.bf16_round(rng.standard_normal((n_cells, KR + Rr))).astype(np.float64)
+    perm = rng.permutation(n_cells)
+    cell_seq, cell_pos = np.full(n_cells, -1), np.full(n_cells, -1)
+    cell_seq[perm[:n_a]], cell_pos[perm[:n_a]] = 1, np.arange(n_a)
+    cell_seq[perm[n_a:T]], cell_pos[perm[n_a:T]] = 0, np.arange(n_b)
+    toks = [(1, p) for p in range(n_a)] + [(0, p) for p in range(n_b)]
+    q_lat = R.bf16_round(rng.standard_normal((T, Hh, KR))).astype(np.float64)
+    q_rot = R.bf16_round(rng.standard_normal((T, Hh, max(Rr, 1)))).astype(np.float64)[..., :Rr]
+    sink = rng.standard_normal(Hh)
+    scale = 1.5 / math.sqrt(KR)
+    dirty = rows.copy()
+    dirty[perm[T:]] = np.nan
+    got = run_latent_attn(q_lat, q_rot, dirty, cell_seq, cell_pos, [s for s, _ in toks], [p for _, p in toks], sink, scale, window, bf16=1)
+    exact = run_latent_attn(q_lat, q_rot, dirty, cell_seq, cell_pos, [s for s, _ in toks], [p for _, p in toks], sink, scale, window, bf16=0)
+    assert np.isfinite(got).all()
+    at = 0
+    for sq, n in ((1, n_a), (0, n_b)):
+        seq_rows = np.stack([rows[np.where((cell_seq == sq) & (cell_pos == j))[0][0]] for j in range(n)])
+        k = np.repeat(seq_rows[:, None, :], Hh, 1)
+        q = np.concatenate([q_lat[at:at + n], q_rot[at:at + n]], -1)
+        want = R.sink_softmax_attention(q, k, k[..., :KR], scale, sink, window)
+        assert rel(exact[at:at + n], want) < 1e-5, sq
+        assert rel(got[at:at + n], want) < 6e-3, sq
+        assert np.abs(got[at:at + n] - want).mean() < 1e-3 * np.abs(want).mean() + 1e-4, sq  # a wrong cell or row moves far more than rounding does
         at += n
 
 
