@@ -208,7 +208,10 @@ static int launch_latent_attn_tile(const b200_latent_attn_args *a, cudaStream_t 
 // w, w + LM_WARPS, ...), NJ groups per warp, which keeps the f32 accumulators of a 16 x kv_rank result within the register file.
 // A tile none of whose cells is visible to any of the 16 tokens is skipped before it is loaded; rows of free cells are read as zeros
 // (their weight is zero, and zero times whatever an unwritten row holds must not reach the sum).
-constexpr int LM_TOK = 16, LM_CELLS = 16, LM_WARPS = 4;
+// The rows of the next visible tile are fetched into registers before the current tile is worked on (warp w fetches cells w and
+// w + 8, a lane every 32nd float4 of a row: NI = ceil(row / 128 floats) loads per row and lane), so the trip to L2 overlaps the
+// tensor-core work instead of standing in front of it.  NI also bounds the column groups per warp: kv_rank / 16 <= 8 NI.
+constexpr int LM_TOK = 16, LM_CELLS = 16, LM_WARPS = 8, LM_PT_STRIDE = 48;
 __device__ __forceinline__ void lm_ldsm4(unsigned addr, unsigned &r0, unsigned &r1, unsigned &r2, unsigned &r3) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
 }
@@ -224,8 +227,8 @@ __device__ __forceinline__ unsigned lm_pack_bf2(float lo, float hi) {
     return *reinterpret_cast<const unsigned *>(&v);
 }
 
-template <int NJ>
-__global__ void __launch_bounds__(LM_WARPS * 32) latent_attn_mma_kernel(const b200_latent_attn_args a) {
+template <int NI>
+__global__ void __launch_bounds__(LM_WARPS * 32, NI <= 5 ? 2 : 1) latent_attn_mma_kernel(const b200_latent_attn_args a) {
     extern __shared__ float4 lm_smem4[];
     const int KR = a.kv_rank, RS = KR + a.rot_dim, RS16 = (RS + 15) & ~15, NK = RS16 / 16, NJG = KR / 16;
     const int stride = RS16 * 2 + 16;  // bytes per bf16 row: 8 consecutive rows start in 8 different 16-byte bank groups (ldmatrix)
@@ -233,6 +236,8 @@ __global__ void __launch_bounds__(LM_WARPS * 32) latent_attn_mma_kernel(const b2
     unsigned char *ts = qs + LM_TOK * stride;                         // [LM_CELLS][stride]
     float *sp = reinterpret_cast<float *>(ts + LM_CELLS * stride);    // [LM_WARPS][32 lanes][8]: partial score tiles in accumulator layout
     int *tseq = reinterpret_cast<int *>(sp + LM_WARPS * 256), *tpos = tseq + LM_TOK, *tlo = tpos + LM_TOK, *cseq = tlo + LM_TOK, *cpos = cseq + LM_CELLS;
+    float *alph = reinterpret_cast<float *>(cpos + LM_CELLS);           // [LM_TOK]: what a row's accumulators are scaled by at this tile; at the end its final weight
+    unsigned char *pt = reinterpret_cast<unsigned char *>(alph + LM_TOK);  // [LM_TOK][LM_PT_STRIDE]: the tile's weights as bf16 (the A operand of the second product)
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
     const int t0 = blockIdx.x * LM_TOK, h = blockIdx.y;
 
@@ -254,17 +259,21 @@ __global__ void __launch_bounds__(LM_WARPS * 32) latent_attn_mma_kernel(const b2
         *reinterpret_cast<__nv_bfloat16 *>(qs + i * stride + j * 2) = __float2bfloat16_rn(v);
     }
     __syncthreads();
-    int rs[2], rp[2], rl[2];
-#pragma unroll
-    for (int hh = 0; hh < 2; hh++) { rs[hh] = tseq[g + 8 * hh]; rp[hh] = tpos[g + 8 * hh]; rl[hh] = tlo[g + 8 * hh]; }
-
     // ldmatrix lane addresses: matrix mi = lane >> 3, row mr = lane & 7
     const int mi = lane >> 3, mr = lane & 7;
     const unsigned qs_u = (unsigned)__cvta_generic_to_shared(qs), ts_u = (unsigned)__cvta_generic_to_shared(ts);
     const unsigned a_off = (unsigned)(((mi & 1) * 8 + mr) * stride + (mi >> 1) * 16);  // A (queries) and transposed B (values): rows (mi&1)*8.., columns (mi>>1)*8..
     const unsigned k_off = (unsigned)(((mi >> 1) * 8 + mr) * stride + (mi & 1) * 16);  // B (keys): cells (mi>>1)*8.., values (mi&1)*8..
 
-    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};  // l: this lane's share (its 4 cells of every tile)
+    // softmax bookkeeping: warp w owns token rows 2 w and 2 w + 1, a lane one (row, cell of the tile) pair; m and l of the row are
+    // the same in its 16 lanes
+    const int my_r = 2 * warp + (lane >> 4), my_u = lane & 15;
+    const int my_seq = tseq[my_r], my_pos = tpos[my_r], my_lo = tlo[my_r];
+    const int sp_off = ((my_r & 7) * 4 + ((my_u & 7) >> 1)) * 8 + (my_u >> 3) * 4 + (my_r >> 3) * 2 + (my_u & 1);  // the pair's place in a partial tile
+    const unsigned pt_u = (unsigned)__cvta_generic_to_shared(pt);
+    const unsigned p_off = (unsigned)(((mi & 1) * 8 + mr) * LM_PT_STRIDE + (mi >> 1) * 16);
+    float m_row = -INFINITY, l_row = 0.f;
+    constexpr int NJ = NI;
     float o[NJ][2][4];
 #pragma unroll
     for (int jj = 0; jj < NJ; jj++)
@@ -272,28 +281,55 @@ __global__ void __launch_bounds__(LM_WARPS * 32) latent_attn_mma_kernel(const b2
         for (int e = 0; e < 4; e++) o[jj][0][e] = o[jj][1][e] = 0.f;
     const int RS4 = RS / 4, RS16_4 = RS16 / 4;
 
-    for (int c0 = 0; c0 < a.n_kv; c0 += LM_CELLS) {
-        bool any = false;
-        for (int idx = tid; idx < LM_TOK * LM_CELLS; idx += LM_WARPS * 32) {
-            const int i = idx >> 4, c = c0 + (idx & 15);
+    // the first tile from `from` on with a cell that one of the 16 tokens sees (n_kv: none); one (token, cell) pair per thread
+    auto next_tile = [&](int from) {
+        for (int c0 = from; c0 < a.n_kv; c0 += LM_CELLS) {
+            const int i = tid >> 4, c = c0 + (tid & 15);
+            bool any = false;
             if (c < a.n_kv) {
                 const int cp = a.cell_pos[c];
-                any |= a.cell_seq[c] == tseq[i] && cp <= tpos[i] && cp > tlo[i];
+                any = a.cell_seq[c] == tseq[i] && cp <= tpos[i] && cp > tlo[i];
+            }
+            if (__syncthreads_or(any)) return c0;
+        }
+        return a.n_kv;
+    };
+    float4 pf[2][NI];
+    int pf_seq = -1, pf_pos = -1;  // threads < LM_CELLS: the cell's owner and position
+    auto fetch = [&](int c0) {
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            const int c = c0 + warp + 8 * r;
+            const bool ok = c < a.n_kv && a.cell_seq[c] >= 0;
+            const float4 *row = reinterpret_cast<const float4 *>(a.cache + (int64_t)(ok ? c : 0) * a.cache_stride);
+#pragma unroll
+            for (int i = 0; i < NI; i++) {
+                const int j = lane + 32 * i;
+                pf[r][i] = ok && j < RS4 ? row[j] : make_float4(0.f, 0.f, 0.f, 0.f);
             }
         }
-        if (!__syncthreads_or(any)) continue;  // also: the previous tile, its scores and its cell table have been read
         if (tid < LM_CELLS) {
             const int c = c0 + tid;
-            cseq[tid] = c < a.n_kv ? a.cell_seq[c] : -1;
-            cpos[tid] = c < a.n_kv ? a.cell_pos[c] : -1;
+            pf_seq = c < a.n_kv ? a.cell_seq[c] : -1;
+            pf_pos = c < a.n_kv ? a.cell_pos[c] : -1;
         }
-        for (int idx = tid; idx < LM_CELLS * RS16_4; idx += LM_WARPS * 32) {
-            const int u = idx / RS16_4, j = idx - u * RS16_4, c = c0 + u;
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (j < RS4 && c < a.n_kv && a.cell_seq[c] >= 0) v = reinterpret_cast<const float4 *>(a.cache + (int64_t)c * a.cache_stride)[j];
-            *reinterpret_cast<uint2 *>(ts + u * stride + j * 8) = make_uint2(lm_pack_bf2(v.x, v.y), lm_pack_bf2(v.z, v.w));
-        }
+    };
+    int c0 = next_tile(0);
+    if (c0 < a.n_kv) fetch(c0);
+    while (c0 < a.n_kv) {
+        __syncthreads();  // the previous tile, its scores and its cell table have been read
+#pragma unroll
+        for (int r = 0; r < 2; r++)
+#pragma unroll
+            for (int i = 0; i < NI; i++) {
+                const int j = lane + 32 * i;
+                if (j < RS16_4)
+                    *reinterpret_cast<uint2 *>(ts + (warp + 8 * r) * stride + j * 8) = make_uint2(lm_pack_bf2(pf[r][i].x, pf[r][i].y), lm_pack_bf2(pf[r][i].z, pf[r][i].w));
+            }
+        if (tid < LM_CELLS) { cseq[tid] = pf_seq; cpos[tid] = pf_pos; }
         __syncthreads();
+        c0 = next_tile(c0 + LM_CELLS);
+        if (c0 < a.n_kv) fetch(c0);  // in flight while this tile is worked on
         float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
         for (int ks = warp; ks < NK; ks += LM_WARPS) {
             unsigned qa[4], b0, b1, b2, b3;
@@ -308,41 +344,31 @@ __global__ void __launch_bounds__(LM_WARPS * 32) latent_attn_mma_kernel(const b2
             mine[1] = make_float4(s[1][0], s[1][1], s[1][2], s[1][3]);
         }
         __syncthreads();
+        {
+            float sv = 0.f;
 #pragma unroll
-        for (int e = 0; e < 4; e++) s[0][e] = s[1][e] = 0.f;
+            for (int w = 0; w < LM_WARPS; w++) sv += sp[w * 256 + sp_off];
+            const int cp = cpos[my_u];
+            const bool vis = cseq[my_u] == my_seq && cp <= my_pos && cp > my_lo;
+            sv = vis ? sv * a.scale : -INFINITY;
+            float mx = sv;
 #pragma unroll
-        for (int w = 0; w < LM_WARPS; w++) {  // the same order in every warp: all hold the same sums
-            const float4 *part = reinterpret_cast<const float4 *>(sp + (w * 32 + lane) * 8);
-            const float4 p0 = part[0], p1 = part[1];
-            s[0][0] += p0.x; s[0][1] += p0.y; s[0][2] += p0.z; s[0][3] += p0.w;
-            s[1][0] += p1.x; s[1][1] += p1.y; s[1][2] += p1.z; s[1][3] += p1.w;
-        }
-        // s[nb][2 hh + e]: token row g + 8 hh, cell 8 nb + 2 t4 + e
-        unsigned pa[4];
-        float alpha[2];
-#pragma unroll
-        for (int hh = 0; hh < 2; hh++) {
-#pragma unroll
-            for (int nb = 0; nb < 2; nb++)
-#pragma unroll
-                for (int e = 0; e < 2; e++) {
-                    const int u = 8 * nb + 2 * t4 + e, cp = cpos[u];
-                    const bool vis = cseq[u] == rs[hh] && cp <= rp[hh] && cp > rl[hh];
-                    s[nb][2 * hh + e] = vis ? s[nb][2 * hh + e] * a.scale : -INFINITY;
-                }
-            float mx = fmaxf(fmaxf(s[0][2 * hh], s[0][2 * hh + 1]), fmaxf(s[1][2 * hh], s[1][2 * hh + 1]));
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-            const float mn = fmaxf(m[hh], mx);
+            for (int off = 1; off < 16; off <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));  // over the row's 16 lanes
+            const float mn = fmaxf(m_row, mx);
             const bool none = mn == -INFINITY;  // nothing seen so far by this row
-            alpha[hh] = none ? 1.0f : expf(m[hh] - mn);
-            const float p0 = none ? 0.f : expf(s[0][2 * hh] - mn), p1 = none ? 0.f : expf(s[0][2 * hh + 1] - mn);
-            const float p2 = none ? 0.f : expf(s[1][2 * hh] - mn), p3 = none ? 0.f : expf(s[1][2 * hh + 1] - mn);
-            l[hh] = l[hh] * alpha[hh] + ((p0 + p1) + (p2 + p3));
-            m[hh] = mn;
-            pa[hh] = lm_pack_bf2(p0, p1);      // a0 / a1: row g (+8), cells 2 t4, 2 t4 + 1
-            pa[2 + hh] = lm_pack_bf2(p2, p3);  // a2 / a3: cells 8 + 2 t4, ...
+            const float al = none ? 1.0f : expf(m_row - mn), pw = none ? 0.f : expf(sv - mn);
+            float ps = pw;
+#pragma unroll
+            for (int off = 1; off < 16; off <<= 1) ps += __shfl_xor_sync(0xffffffffu, ps, off);
+            l_row = l_row * al + ps;
+            m_row = mn;
+            *reinterpret_cast<__nv_bfloat16 *>(pt + my_r * LM_PT_STRIDE + my_u * 2) = __float2bfloat16_rn(pw);
+            if (my_u == 0) alph[my_r] = al;
         }
+        __syncthreads();
+        unsigned pa[4];
+        lm_ldsm4(pt_u + p_off, pa[0], pa[1], pa[2], pa[3]);
+        const float alpha[2] = {alph[g], alph[g + 8]};
         const bool rescale = __any_sync(0xffffffffu, alpha[0] != 1.0f || alpha[1] != 1.0f);
 #pragma unroll
         for (int jj = 0; jj < NJ; jj++) {
@@ -358,18 +384,16 @@ __global__ void __launch_bounds__(LM_WARPS * 32) latent_attn_mma_kernel(const b2
             lm_mma_bf16(o[jj][1], pa, b2, b3);  // columns 16 j + 8 .. 16 j + 15
         }
     }
-    const float sink = a.sink ? a.sink[h] : -INFINITY;
-    float w[2];
-#pragma unroll
-    for (int hh = 0; hh < 2; hh++) {
-        float lt = l[hh];
-        lt += __shfl_xor_sync(0xffffffffu, lt, 1);
-        lt += __shfl_xor_sync(0xffffffffu, lt, 2);
-        const float M = fmaxf(m[hh], sink);
-        const float f = m[hh] == -INFINITY ? 0.f : expf(m[hh] - M);
-        const float den = lt * f + (a.sink ? expf(sink - M) : 0.f);
-        w[hh] = den > 0.f ? f / den : 0.f;
+    __syncthreads();  // the last tile's scale factors have been read
+    if (my_u == 0) {
+        const float sink = a.sink ? a.sink[h] : -INFINITY;
+        const float M = fmaxf(m_row, sink);
+        const float f = m_row == -INFINITY ? 0.f : expf(m_row - M);
+        const float den = l_row * f + (a.sink ? expf(sink - M) : 0.f);
+        alph[my_r] = den > 0.f ? f / den : 0.f;
     }
+    __syncthreads();
+    const float w[2] = {alph[g], alph[g + 8]};
 #pragma unroll
     for (int jj = 0; jj < NJ; jj++) {
         const int j = warp + jj * LM_WARPS;
@@ -387,14 +411,14 @@ __global__ void __launch_bounds__(LM_WARPS * 32) latent_attn_mma_kernel(const b2
 
 static size_t latent_attn_mma_smem(const b200_latent_attn_args *a) {
     const int rs16 = (a->kv_rank + a->rot_dim + 15) & ~15;
-    return (size_t)(LM_TOK + LM_CELLS) * (rs16 * 2 + 16) + (size_t)LM_WARPS * 256 * 4 + (3 * LM_TOK + 2 * LM_CELLS) * 4;
+    return (size_t)(LM_TOK + LM_CELLS) * (rs16 * 2 + 16) + (size_t)LM_WARPS * 256 * 4 + (3 * LM_TOK + 2 * LM_CELLS + LM_TOK) * 4 + LM_TOK * LM_PT_STRIDE;
 }
-template <int NJ>
+template <int NI>
 static int launch_latent_attn_mma2(const b200_latent_attn_args *a, cudaStream_t st) {
     const dim3 grid((unsigned)((a->n_tokens + LM_TOK - 1) / LM_TOK), (unsigned)a->n_head);
     const size_t smem = latent_attn_mma_smem(a);
-    if (smem > 48 * 1024) B200_CUDA_TRY(cudaFuncSetAttribute(latent_attn_mma_kernel<NJ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    latent_attn_mma_kernel<NJ><<<grid, LM_WARPS * 32, smem, st>>>(*a);
+    if (smem > 48 * 1024) B200_CUDA_TRY(cudaFuncSetAttribute(latent_attn_mma_kernel<NI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    latent_attn_mma_kernel<NI><<<grid, LM_WARPS * 32, smem, st>>>(*a);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
 }
@@ -404,12 +428,13 @@ static bool latent_attn_mma_ok(const b200_latent_attn_args *a) {
            ((uintptr_t)a->cache & 15) == 0 && latent_attn_mma_smem(a) <= 200 * 1024;
 }
 static int launch_latent_attn_mma(const b200_latent_attn_args *a, cudaStream_t st) {
-    const int nj = (a->kv_rank / 16 + LM_WARPS - 1) / LM_WARPS;
-    if (nj <= 1) return launch_latent_attn_mma2<1>(a, st);
-    if (nj <= 2) return launch_latent_attn_mma2<2>(a, st);
-    if (nj <= 4) return launch_latent_attn_mma2<4>(a, st);
-    if (nj <= 8) return launch_latent_attn_mma2<8>(a, st);
-    return launch_latent_attn_mma2<16>(a, st);
+    const int ni = (((a->kv_rank + a->rot_dim + 15) & ~15) + 127) / 128;  // <= 9 for kv_rank <= 1024, rot_dim <= 128
+    if (ni <= 1) return launch_latent_attn_mma2<1>(a, st);
+    if (ni <= 2) return launch_latent_attn_mma2<2>(a, st);
+    if (ni <= 3) return launch_latent_attn_mma2<3>(a, st);
+    if (ni <= 5) return launch_latent_attn_mma2<5>(a, st);
+    if (ni <= 7) return launch_latent_attn_mma2<7>(a, st);
+    return launch_latent_attn_mma2<9>(a, st);
 }
 
 template <int NL, int NR, int WARPS>
