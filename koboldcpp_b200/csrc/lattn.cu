@@ -238,6 +238,7 @@ __global__ void __launch_bounds__(LM_WARPS * 32, NI <= 5 ? 2 : 1) latent_attn_mm
     int *tseq = reinterpret_cast<int *>(sp + LM_WARPS * 256), *tpos = tseq + LM_TOK, *tlo = tpos + LM_TOK, *cseq = tlo + LM_TOK, *cpos = cseq + LM_CELLS;
     float *alph = reinterpret_cast<float *>(cpos + LM_CELLS);           // [LM_TOK]: what a row's accumulators are scaled by at this tile; at the end its final weight
     unsigned char *pt = reinterpret_cast<unsigned char *>(alph + LM_TOK);  // [LM_TOK][LM_PT_STRIDE]: the tile's weights as bf16 (the A operand of the second product)
+    unsigned *tbits = reinterpret_cast<unsigned *>(pt + LM_TOK * LM_PT_STRIDE);  // one bit per tile of cells: something to see there
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
     const int t0 = blockIdx.x * LM_TOK, h = blockIdx.y;
 
@@ -249,16 +250,46 @@ __global__ void __launch_bounds__(LM_WARPS * 32, NI <= 5 ? 2 : 1) latent_attn_mm
         tpos[tid] = p;
         tlo[tid] = a.window > 0 ? p - a.window : INT_MIN;
     }
-    for (int idx = tid; idx < LM_TOK * RS16; idx += LM_WARPS * 32) {
-        const int i = idx / RS16, j = idx - i * RS16, t = t0 + i;
-        float v = 0.f;
-        if (t < a.n_tokens) {
-            if (j < KR) v = a.q_lat[(int64_t)h * a.q_lat_s_head + (int64_t)t * a.q_lat_s_tok + j];
-            else if (j < RS) v = a.q_rot[(int64_t)h * a.q_rot_s_head + (int64_t)t * a.q_rot_s_tok + (j - KR)];
+    // queries: warp w stages token rows w and w + 8, four loads in flight per lane
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+        const int i = warp + 8 * r, t = t0 + i;
+        const bool ok = t < a.n_tokens;
+        const float *ql = a.q_lat + (int64_t)h * a.q_lat_s_head + (int64_t)(ok ? t : 0) * a.q_lat_s_tok;
+        const float *qr = a.q_rot ? a.q_rot + (int64_t)h * a.q_rot_s_head + (int64_t)(ok ? t : 0) * a.q_rot_s_tok : a.q_lat;
+        for (int j0 = lane; j0 < RS16; j0 += 128) {
+            float v[4];
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const int j = j0 + 32 * k;
+                v[k] = !ok || j >= RS ? 0.f : j < KR ? ql[j] : qr[j - KR];
+            }
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const int j = j0 + 32 * k;
+                if (j < RS16) *reinterpret_cast<__nv_bfloat16 *>(qs + i * stride + j * 2) = __float2bfloat16_rn(v[k]);
+            }
         }
-        *reinterpret_cast<__nv_bfloat16 *>(qs + i * stride + j * 2) = __float2bfloat16_rn(v);
+    }
+    // which tiles hold a cell that one of the 16 tokens sees: one bit per tile, found once, warp w looks at tiles w, w + 8, ...;
+    // a lane takes one cell of the tile against 8 of the tokens
+    const int n_tiles = (a.n_kv + LM_CELLS - 1) / LM_CELLS;
+    for (int i = tid; i < (n_tiles + 31) / 32; i += LM_WARPS * 32) tbits[i] = 0u;
+    __syncthreads();
+    for (int tile = warp; tile < n_tiles; tile += LM_WARPS) {
+        const int c = tile * LM_CELLS + (lane & 15), i0 = (lane >> 4) * 8;
+        bool any = false;
+        if (c < a.n_kv) {
+            const int cs = a.cell_seq[c], cp = a.cell_pos[c];
+            if (cs >= 0) {
+#pragma unroll
+                for (int i = i0; i < i0 + 8; i++) any |= cs == tseq[i] && cp <= tpos[i] && cp > tlo[i];
+            }
+        }
+        if (__ballot_sync(0xffffffffu, any) != 0u && lane == 0) atomicOr(&tbits[tile >> 5], 1u << (tile & 31));
     }
     __syncthreads();
+
     // ldmatrix lane addresses: matrix mi = lane >> 3, row mr = lane & 7
     const int mi = lane >> 3, mr = lane & 7;
     const unsigned qs_u = (unsigned)__cvta_generic_to_shared(qs), ts_u = (unsigned)__cvta_generic_to_shared(ts);
@@ -281,16 +312,13 @@ __global__ void __launch_bounds__(LM_WARPS * 32, NI <= 5 ? 2 : 1) latent_attn_mm
         for (int e = 0; e < 4; e++) o[jj][0][e] = o[jj][1][e] = 0.f;
     const int RS4 = RS / 4, RS16_4 = RS16 / 4;
 
-    // the first tile from `from` on with a cell that one of the 16 tokens sees (n_kv: none); one (token, cell) pair per thread
+    // the first tile from `from` on with a cell that one of the 16 tokens sees (n_kv: none)
     auto next_tile = [&](int from) {
-        for (int c0 = from; c0 < a.n_kv; c0 += LM_CELLS) {
-            const int i = tid >> 4, c = c0 + (tid & 15);
-            bool any = false;
-            if (c < a.n_kv) {
-                const int cp = a.cell_pos[c];
-                any = a.cell_seq[c] == tseq[i] && cp <= tpos[i] && cp > tlo[i];
-            }
-            if (__syncthreads_or(any)) return c0;
+        int tile = from / LM_CELLS;
+        while (tile < n_tiles) {
+            const unsigned rest = tbits[tile >> 5] >> (tile & 31);
+            if (rest) return (tile + __ffs(rest) - 1) * LM_CELLS;
+            tile = (tile | 31) + 1;
         }
         return a.n_kv;
     };
@@ -411,7 +439,8 @@ __global__ void __launch_bounds__(LM_WARPS * 32, NI <= 5 ? 2 : 1) latent_attn_mm
 
 static size_t latent_attn_mma_smem(const b200_latent_attn_args *a) {
     const int rs16 = (a->kv_rank + a->rot_dim + 15) & ~15;
-    return (size_t)(LM_TOK + LM_CELLS) * (rs16 * 2 + 16) + (size_t)LM_WARPS * 256 * 4 + (3 * LM_TOK + 2 * LM_CELLS + LM_TOK) * 4 + LM_TOK * LM_PT_STRIDE;
+    return (size_t)(LM_TOK + LM_CELLS) * (rs16 * 2 + 16) + (size_t)LM_WARPS * 256 * 4 + (3 * LM_TOK + 2 * LM_CELLS + LM_TOK) * 4 + LM_TOK * LM_PT_STRIDE +
+           (size_t)(((a->n_kv + LM_CELLS - 1) / LM_CELLS + 31) / 32) * 4;
 }
 template <int NI>
 static int launch_latent_attn_mma2(const b200_latent_attn_args *a, cudaStream_t st) {
