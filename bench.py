@@ -769,7 +769,7 @@ def main() -> int:
     ap.add_argument("--no-tp70", action="store_true", default=bool(os.environ.get("B200_BENCH_NO_TP70")),
                     help="skip the auxiliary 70B tensor-parallel leg (BASELINE.json configs[4])")
     ap.add_argument("--design", default="", choices=["", "genesun"],
-                    help="instead of the round benchmark: prefill / decode of this design at real layer shapes beside the llama decoder at equal size")
+                    help="instead of the default workload: prefill / decode of this design at real layer shapes beside the llama decoder at equal size")
     ap.add_argument("--design-sizes", default="", help="comma-separated subset of " + ",".join(DESIGN_SIZES))
     args = ap.parse_args()
     if args.design:

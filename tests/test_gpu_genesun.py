@@ -476,6 +476,30 @@ def test_bfloat16_weights_close_to_float32():
     assert np.quantile(e, 0.9) < 2e-2 and e.max() < 0.5
 
 
+def test_bfloat16_portions_and_batches_agree_with_the_whole_prompt():
+    """bf16 serving mode: prompt portions of 16 tokens or more take the tensor-core attention, over cells that earlier portions
+    wrote and beside another request's tokens; shorter portions and single tokens take the f32 kernels.  All of them must
+    give the logits of the whole prompt up to bf16 rounding."""
+    cfg = CONFIGS["mixed"]()
+    W = R.random_weights(cfg, seed=5)
+    rng = np.random.default_rng(1)
+    ta, tb = rng.integers(0, cfg["vocab"], 75).tolist(), rng.integers(0, cfg["vocab"], 41).tolist()
+    m = G.build(cfg, R.as_tensors(W), dtype="bfloat16", n_ctx=256, n_seq_max=2, max_batch=128)
+    eng = Engine(m)
+    whole = eng.step([("a", ta, range(75))])
+    eng.finish("a")
+    parts = [eng.step([("b", tb, []), ("a", ta[:33], range(33))])]  # the freed cells are used again, in another order
+    parts.append(eng.step([("a", ta[33:53], range(20))]))
+    parts.append(eng.step([("a", ta[53:70], range(17))]))
+    parts.append(eng.step([("a", ta[70:73], range(3))]))
+    parts += [eng.step([("a", [t], [0])]) for t in ta[73:]]
+    m.close()
+    d = np.concatenate(parts) - whole
+    d = d - d.mean(-1, keepdims=True)
+    e = np.sqrt((d ** 2).mean(-1)) / whole.std()
+    assert np.isfinite(e).all() and np.quantile(e, 0.9) < 2e-2 and e.max() < 0.5
+
+
 def test_far_key_through_the_model():
     """Weights make the attention sharp (large score scale), so a wrong position, mask or cell would show in the logits."""
     cfg = R.make_config([R.attn_layer(heads=2, dim=16, rot_dim=8, kv_rank=32, q_rank=32, ff=0), R.attn_layer(kv_from=0, ff=32)])
