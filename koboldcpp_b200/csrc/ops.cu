@@ -739,11 +739,93 @@ __global__ void __launch_bounds__(GW_WARPS * 32) gemv_bf16_wide_kernel(const uns
     }
 }
 
+// Three to eight activation rows with K a multiple of 32: the tensor cores take the contraction (mma.sync.m16n8k16, bf16 in, f32
+// accumulators), 16 weight rows as A against the activation rows as the 8 columns of B (rounded to bf16 as the GEMM for larger
+// batches rounds them; columns past the batch are zero).  No shared-memory staging: a lane's 16-byte load of a weight row is 8
+// consecutive k, and the same 8 k of activation row g go into its B registers -- any one-to-one assignment of k to fragment
+// slots is a valid contraction as long as A and B agree, so two mma cover a block of 32 k.  The warps of a CTA split K (a matrix of a few
+// thousand rows gives only a CTA or two per SM: the loads in flight have to come from the warps of each).
+constexpr int GM_WARPS = 8, GM_TILES = 1, GM_ROWS = 16 * GM_TILES, GM_RUN = 4;
+__device__ __forceinline__ unsigned gm_pack_bf2(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const unsigned *>(&v);
+}
+__device__ __forceinline__ void gm_mma_bf16(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// A CTA takes GM_TILES tiles of 16 weight rows (one: more and smaller CTAs keep more loads in flight, measured against two).
+__global__ void __launch_bounds__(GM_WARPS * 32) gemv_bf16_mma_kernel(const unsigned char *__restrict__ W, int64_t w_row_bytes, int64_t w_batch_bytes, const float *__restrict__ X,
+                                                                      int64_t x_stride, int64_t x_batch, float *__restrict__ dst, int64_t dst_stride, int64_t dst_batch,
+                                                                      int64_t K, int64_t M, int nc) {
+    __shared__ float part[GM_WARPS][GM_ROWS * 8];
+    const int64_t m0 = (int64_t)blockIdx.x * GM_ROWS;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+    W += (int64_t)blockIdx.y * w_batch_bytes; X += (int64_t)blockIdx.y * x_batch; dst += (int64_t)blockIdx.y * dst_batch;
+    // rows past M repeat the last row: computed and dropped
+    const uint4 *w0[GM_TILES], *w1[GM_TILES];
+#pragma unroll
+    for (int t = 0; t < GM_TILES; t++) {
+        const int64_t r = m0 + 16 * t + g;
+        w0[t] = reinterpret_cast<const uint4 *>(W + (r < M ? r : M - 1) * w_row_bytes);
+        w1[t] = reinterpret_cast<const uint4 *>(W + (r + 8 < M ? r + 8 : M - 1) * w_row_bytes);
+    }
+    const bool col_ok = g < nc;
+    const float4 *xc = reinterpret_cast<const float4 *>(X + (col_ok ? g : 0) * x_stride);
+    float acc[GM_TILES][4];
+#pragma unroll
+    for (int t = 0; t < GM_TILES; t++) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
+    const int64_t nblk = K / 32;
+    // a warp takes runs of GM_RUN consecutive blocks (GM_RUN x 64 bytes of every row, requested back to back), all loads of a run first
+    for (int64_t b0 = (int64_t)warp * GM_RUN; b0 < nblk; b0 += GM_WARPS * GM_RUN) {
+        uint4 a0[GM_RUN][GM_TILES], a1[GM_RUN][GM_TILES];
+        float4 x0[GM_RUN], x1[GM_RUN];
+#pragma unroll
+        for (int u = 0; u < GM_RUN; u++) {
+            const bool in = b0 + u < nblk;
+            const int64_t i = (in ? b0 + u : b0) * 4 + t4;  // k = 32 b + 8 t4 .. + 7
+#pragma unroll
+            for (int t = 0; t < GM_TILES; t++) { a0[u][t] = ld_stream16(w0[t] + i); a1[u][t] = ld_stream16(w1[t] + i); }
+            x0[u] = x1[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (col_ok && in) { x0[u] = xc[2 * i]; x1[u] = xc[2 * i + 1]; }  // a block past the end: zero activations
+        }
+#pragma unroll
+        for (int u = 0; u < GM_RUN; u++) {
+            const unsigned b0r = gm_pack_bf2(x0[u].x, x0[u].y), b1r = gm_pack_bf2(x0[u].z, x0[u].w), b2r = gm_pack_bf2(x1[u].x, x1[u].y), b3r = gm_pack_bf2(x1[u].z, x1[u].w);
+#pragma unroll
+            for (int t = 0; t < GM_TILES; t++) {
+                gm_mma_bf16(acc[t], a0[u][t].x, a1[u][t].x, a0[u][t].y, a1[u][t].y, b0r, b1r);
+                gm_mma_bf16(acc[t], a0[u][t].z, a1[u][t].z, a0[u][t].w, a1[u][t].w, b2r, b3r);
+            }
+        }
+    }
+    // acc[t][0], [1]: weight row 16 t + g, activation rows 2 t4, 2 t4 + 1; acc[t][2], [3]: weight row 16 t + g + 8
+#pragma unroll
+    for (int t = 0; t < GM_TILES; t++) {
+        part[warp][(16 * t + g) * 8 + 2 * t4] = acc[t][0]; part[warp][(16 * t + g) * 8 + 2 * t4 + 1] = acc[t][1];
+        part[warp][(16 * t + g + 8) * 8 + 2 * t4] = acc[t][2]; part[warp][(16 * t + g + 8) * 8 + 2 * t4 + 1] = acc[t][3];
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < GM_ROWS * 8; idx += GM_WARPS * 32) {
+        const int r = idx >> 3, c = idx & 7;  // one (weight row, activation row) pair
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < GM_WARPS; w++) v += part[w][idx];
+        if (c < nc && m0 + r < M) dst[c * dst_stride + m0 + r] = v;
+    }
+}
+
 template <int NC>
 static void launch_gemv_bf16(const b200_tensor *w, const b200_tensor *x, const b200_tensor *dst, cudaStream_t st) {
     const int64_t M = w->ne[1], nb = x->ne[2];
     const int64_t wb = w->ne[2] > 1 ? (int64_t)w->nb[2] : 0;
     if constexpr (NC >= 3) {
+        if (w->ne[0] % 32 == 0) {
+            const dim3 grid((unsigned)((M + GM_ROWS - 1) / GM_ROWS), (unsigned)nb);
+            gemv_bf16_mma_kernel<<<grid, GM_WARPS * 32, 0, st>>>((const unsigned char *)w->data, (int64_t)w->nb[1], wb, (const float *)x->data, (int64_t)(x->nb[1] / 4),
+                                                                 (int64_t)(x->nb[2] / 4), (float *)dst->data, (int64_t)(dst->nb[1] / 4), (int64_t)(dst->nb[2] / 4), w->ne[0], M, NC);
+            return;
+        }
         const dim3 grid((unsigned)((M + GW_ROWS - 1) / GW_ROWS), (unsigned)nb);
         gemv_bf16_wide_kernel<NC><<<grid, GW_WARPS * 32, 0, st>>>((const unsigned char *)w->data, (int64_t)w->nb[1], wb, (const float *)x->data, (int64_t)(x->nb[1] / 4),
                                                                   (int64_t)(x->nb[2] / 4), (float *)dst->data, (int64_t)(dst->nb[1] / 4), (int64_t)(dst->nb[2] / 4), w->ne[0], M);

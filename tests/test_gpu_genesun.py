@@ -287,10 +287,12 @@ def test_mlstm_gates_saturate_without_overflow():
     assert np.isfinite(got).all() and rel(got, want) < 5e-5
 
 
-@pytest.mark.parametrize("K,M,N", [(64, 5, 1), (320, 37, 3), (4096, 130, 8), (200, 9, 2), (100, 7, 1), (128, 300, 9), (320, 257, 40), (2048, 512, 300), (192, 64, 513)])
+@pytest.mark.parametrize("K,M,N", [(64, 5, 1), (320, 37, 3), (4096, 130, 8), (200, 9, 2), (100, 7, 1), (128, 300, 9), (320, 257, 40), (2048, 512, 300), (192, 64, 513),
+                                   (96, 21, 5), (200, 9, 4), (32, 16, 8), (2048, 47, 6), (104, 33, 7)])
 def test_dense_bf16_matmul(K, M, N):
-    """N <= 8: the GEMV with f32 activations (K not a multiple of 8 falls back to the plain kernel); larger N: the tensor-core
-    GEMM, whose activations are rounded to bf16."""
+    """N <= 2: the GEMV with f32 activations (K not a multiple of 8 falls back to the plain kernel); N = 3..8: the tensor-core
+    GEMV when K is a multiple of 32 (activations rounded to bf16), else the f32 one; larger N: the tensor-core GEMM, whose
+    activations are rounded to bf16."""
     rng = np.random.default_rng(K + M + N)
     w = R.bf16_round(rng.standard_normal((M, K)))
     x = rng.standard_normal((N, K)).astype(np.float32)
@@ -299,7 +301,8 @@ def test_dense_bf16_matmul(K, M, N):
         dw, dx, dd = dev(bits, np.uint16), dev(x), H.DeviceBuffer(4 * N * M + 256)
         tw, tx, td = Tensor.contiguous(dw.ptr, BF16, (K, M)), Tensor.contiguous(dx.ptr, F32, (K, N)), Tensor.contiguous(dd.ptr, F32, (M, N))
         check(lib().b200_op_mul_mat_float(C.byref(tw), C.byref(tx), C.byref(td), None))
-        got, want = dd.to_numpy(np.float32, (N, M)), x.astype(np.float64) @ w.astype(np.float64).T
+        xr = R.bf16_round(x) if N >= 3 and K % 32 == 0 else x
+        got, want = dd.to_numpy(np.float32, (N, M)), xr.astype(np.float64) @ w.astype(np.float64).T
         assert rel(got, want) < 2e-6
     else:
         got = H.mul_mat_q(BF16, bits.view(np.uint8), x, K, M)
@@ -327,7 +330,8 @@ def test_dense_bf16_matmul_batched(K, M, N, B):
     tx.nb[1], tx.nb[2] = 4 * B * K, 4 * K
     check(lib().b200_op_mul_mat_float(C.byref(tw), C.byref(tx), C.byref(td), None))
     got = dd.to_numpy(np.float32, (B, n8, M))
-    want = np.einsum("nbk,bmk->bnm", x[:n8].astype(np.float64), w.astype(np.float64))
+    xr = R.bf16_round(x[:n8]) if n8 >= 3 and K % 32 == 0 else x[:n8]
+    want = np.einsum("nbk,bmk->bnm", xr.astype(np.float64), w.astype(np.float64))
     assert rel(got, want) < 2e-6
 
 
