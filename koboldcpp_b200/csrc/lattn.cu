@@ -60,45 +60,56 @@ __global__ void __launch_bounds__(WARPS * 32) latent_attn_kernel(const b200_late
     const int seq = a.tok_seq[t], pos = a.tok_pos[t];
     const int lo = a.window > 0 ? pos - a.window : INT_MIN;
     float m = -INFINITY, l = 0.f;
-    for (int c0 = warp * LA_UNROLL; c0 < a.n_kv; c0 += WARPS * LA_UNROLL) {
-        bool vis[LA_UNROLL];
-        float rv[LA_UNROLL][NL], rr[LA_UNROLL][NR];
-#pragma unroll
-        for (int u = 0; u < LA_UNROLL; u++) {
-            const int c = c0 + u;
-            const int cp = c < a.n_kv ? a.cell_pos[c] : -1;
-            vis[u] = c < a.n_kv && a.cell_seq[c] == seq && cp <= pos && cp > lo;  // warp-uniform
+    // a warp looks at 32 cells at a time, one per lane, and then works through the visible ones LA_UNROLL at a time: a cache shared
+    // with other sequences costs one ballot per 32 of their cells, not a round of loads
+    for (int cb = warp * 32; cb < a.n_kv; cb += WARPS * 32) {
+        bool mine = false;
+        if (cb + lane < a.n_kv) {
+            const int cp = a.cell_pos[cb + lane];
+            mine = a.cell_seq[cb + lane] == seq && cp <= pos && cp > lo;
         }
+        unsigned rest = __ballot_sync(0xffffffffu, mine);
+        while (rest) {
+            bool vis[LA_UNROLL];  // warp-uniform
+            int cu[LA_UNROLL];
+            float rv[LA_UNROLL][NL], rr[LA_UNROLL][NR];
 #pragma unroll
-        for (int u = 0; u < LA_UNROLL; u++) {
-            if (!vis[u]) continue;
-            const float *row = a.cache + (int64_t)(c0 + u) * a.cache_stride;
+            for (int u = 0; u < LA_UNROLL; u++) {
+                vis[u] = rest != 0u;
+                cu[u] = vis[u] ? cb + __ffs(rest) - 1 : 0;
+                rest &= rest - 1;  // 0 stays 0
+            }
 #pragma unroll
-            for (int i = 0; i < NL; i++) { const int j = lane + 32 * i; rv[u][i] = j < KR ? row[j] : 0.f; }
+            for (int u = 0; u < LA_UNROLL; u++) {
+                if (!vis[u]) continue;
+                const float *row = a.cache + (int64_t)cu[u] * a.cache_stride;
 #pragma unroll
-            for (int i = 0; i < NR; i++) { const int j = lane + 32 * i; rr[u][i] = j < R ? row[KR + j] : 0.f; }
-        }
-        float s[LA_UNROLL];
+                for (int i = 0; i < NL; i++) { const int j = lane + 32 * i; rv[u][i] = j < KR ? row[j] : 0.f; }
 #pragma unroll
-        for (int u = 0; u < LA_UNROLL; u++) {
-            s[u] = 0.f;
-            if (!vis[u]) continue;
+                for (int i = 0; i < NR; i++) { const int j = lane + 32 * i; rr[u][i] = j < R ? row[KR + j] : 0.f; }
+            }
+            float s[LA_UNROLL];
 #pragma unroll
-            for (int i = 0; i < NL; i++) s[u] += q1[i] * rv[u][i];
+            for (int u = 0; u < LA_UNROLL; u++) {
+                s[u] = 0.f;
+                if (!vis[u]) continue;
 #pragma unroll
-            for (int i = 0; i < NR; i++) s[u] += q2[i] * rr[u][i];
-        }
+                for (int i = 0; i < NL; i++) s[u] += q1[i] * rv[u][i];
 #pragma unroll
-        for (int u = 0; u < LA_UNROLL; u++) if (vis[u]) s[u] = warp_sum(s[u]);
+                for (int i = 0; i < NR; i++) s[u] += q2[i] * rr[u][i];
+            }
 #pragma unroll
-        for (int u = 0; u < LA_UNROLL; u++) {
-            if (!vis[u]) continue;
-            const float mn = fmaxf(m, s[u]);
-            const float corr = expf(m - mn), p = expf(s[u] - mn);  // m = -inf at the first cell: corr = 0
-            l = l * corr + p;
+            for (int u = 0; u < LA_UNROLL; u++) if (vis[u]) s[u] = warp_sum(s[u]);
 #pragma unroll
-            for (int i = 0; i < NL; i++) acc[i] = acc[i] * corr + p * rv[u][i];
-            m = mn;
+            for (int u = 0; u < LA_UNROLL; u++) {
+                if (!vis[u]) continue;
+                const float mn = fmaxf(m, s[u]);
+                const float corr = expf(m - mn), p = expf(s[u] - mn);  // m = -inf at the first cell: corr = 0
+                l = l * corr + p;
+#pragma unroll
+                for (int i = 0; i < NL; i++) acc[i] = acc[i] * corr + p * rv[u][i];
+                m = mn;
+            }
         }
     }
     float *sacc = smem + (size_t)warp * KR, *sm = smem + (size_t)WARPS * KR, *sl = sm + WARPS;
