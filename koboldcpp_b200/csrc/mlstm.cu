@@ -1,8 +1,8 @@
 // mlstm.cu -- matrix-memory recurrence (mLSTM) with a stabilised exponential input gate (include/b200_ggml_ops.h: b200_op_mlstm_scan).
 //
 // Per (sequence, head) the state is a dim x vdim matrix S, a dim vector n and a running maximum m, all f32 and carried from
-// token to token in a slot of the state pool.  The columns of S never interact: a CTA owns 32 columns of one (sequence, head),
-// a warp 4 of them, a lane the rows d = lane, lane + 32, ... -- the state stays in registers for the whole token loop, the
+// token to token in a slot of the state pool.  The columns of S never interact: a CTA owns 16 or 32 columns of one (sequence, head),
+// a warp 2 or 4 of them, a lane the rows d = lane, lane + 32, ... -- the state stays in registers for the whole token loop, the
 // per-token inputs come through shared memory a chunk of tokens at a time.  The sums over the rows (n . q and one numerator per
 // column) do not feed the recurrence, so the token loop only parks each lane's share in shared memory and the warp adds them
 // up for ML_RG tokens at a time, one sum per lane, outside the serial chain.
@@ -12,16 +12,22 @@
 namespace b200 {
 using namespace opx;
 
-constexpr int ML_CW = 4, ML_WARPS = 8, ML_COLS = ML_CW * ML_WARPS, ML_CHUNK = 16, ML_THREADS = ML_WARPS * 32;
-constexpr int ML_RG = 8, ML_NP = ML_CW + 1;  // tokens whose reductions are done together; sums per token (n . q and one numerator per column)
+constexpr int ML_WARPS = 8, ML_CHUNK = 16, ML_THREADS = ML_WARPS * 32;
+constexpr int ML_RG = 8;  // tokens whose reductions are done together
+// A warp owns CW columns (2 or 4: a CTA 16 or 32).  4 does less of the work that every warp repeats (n, n . q); 2 gives twice the
+// CTAs when heads x columns / 32 would leave SMs idle.  n and m belong to the head, not to a column: the state keeps one copy
+// per ML_LAYOUT_COLS columns so that no CTA reads what another CTA of the same launch writes, every copy is the same, and a
+// CTA of 32 columns reads the first of its two copies and writes both -- launches with either CW can follow each other.
+constexpr int ML_LAYOUT_COLS = 16;
 
-// The inputs of ML_CHUNK tokens (q, k of the head, v of the CTA's 32 columns, the two gate values) are fetched by all threads
+// The inputs of ML_CHUNK tokens (q, k of the head, v of the CTA's columns, the two gate values) are fetched by all threads
 // at once into registers while the previous chunk is being processed, then parked in shared memory, with the gate
 // non-linearities (tanh cap, log-sigmoid) already applied by one thread per token: the serial token loop reads shared memory
 // only and pays two exponentials per token, and a chunk costs one round trip to L2 that overlaps the chunk before it.
-template <int DPL>
+template <int DPL, int ML_CW>
 __global__ void __launch_bounds__(ML_THREADS) mlstm_scan_kernel(const b200_mlstm_args a) {
     extern __shared__ float sm_[];
+    constexpr int ML_COLS = ML_CW * ML_WARPS, ML_NP = ML_CW + 1, ML_COPIES = ML_COLS / ML_LAYOUT_COLS;  // ML_NP: sums per token (n . q and one numerator per column)
     const int h = blockIdx.y, s = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
     const int H = a.heads, D = a.dim, V = a.vdim;
@@ -32,11 +38,11 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_scan_kernel(const b200_mlstm
     float *wpart = slf + ML_CHUNK + warp * (ML_RG * ML_NP * 32 + ML_RG * ML_NP + ML_RG), *wred = wpart + ML_RG * ML_NP * 32, *wmn = wred + ML_RG * ML_NP;  // this warp's own
     float S[ML_CW][DPL], nn[DPL], m = 0.f;
     // n and m are kept once per CTA (column tile): a CTA never reads state that another CTA of the same launch writes
-    const int nvt = gridDim.x;
+    const int nvt = (V + ML_LAYOUT_COLS - 1) / ML_LAYOUT_COLS, vt0 = blockIdx.x * ML_COPIES;
     float *base = a.state + (int64_t)slot * a.slot_stride;
     float *Sp = base + ((int64_t)h * V + col0) * D;
-    float *np = base + (int64_t)H * V * D + ((int64_t)h * nvt + blockIdx.x) * D;
-    float *mp = base + (int64_t)H * V * D + (int64_t)H * nvt * D + (int64_t)h * nvt + blockIdx.x;
+    float *np = base + (int64_t)H * V * D + ((int64_t)h * nvt + vt0) * D;
+    float *mp = base + (int64_t)H * V * D + (int64_t)H * nvt * D + (int64_t)h * nvt + vt0;
 #pragma unroll
     for (int i = 0; i < DPL; i++) {
         const int d = lane + 32 * i;
@@ -139,11 +145,11 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_scan_kernel(const b200_mlstm
     for (int i = 0; i < DPL; i++) {
         const int d = lane + 32 * i;
         if (d >= D) continue;
-        if (warp == 0) np[d] = nn[i];
+        if (warp < ML_COPIES && vt0 + warp < nvt) np[(int64_t)warp * D + d] = nn[i];
 #pragma unroll
         for (int c = 0; c < ML_CW; c++) if (col0 + c < V) Sp[(int64_t)c * D + d] = S[c][i];
     }
-    if (warp == 0 && lane == 0) *mp = m;
+    if (warp < ML_COPIES && vt0 + warp < nvt && lane == 0) mp[warp] = m;
 }
 
 }  // namespace b200
@@ -151,7 +157,7 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_scan_kernel(const b200_mlstm
 using namespace b200;
 
 extern "C" int64_t b200_mlstm_state_floats(int32_t heads, int32_t dim, int32_t vdim) {
-    const int64_t nvt = (vdim + ML_COLS - 1) / ML_COLS;
+    const int64_t nvt = (vdim + ML_LAYOUT_COLS - 1) / ML_LAYOUT_COLS;
     return (int64_t)heads * vdim * dim + (int64_t)heads * nvt * dim + (int64_t)heads * nvt;
 }
 
@@ -161,20 +167,29 @@ extern "C" int b200_op_mlstm_scan(const b200_mlstm_args *a, b200_stream_t stream
                 a->slot_stride >= b200_mlstm_state_floats(a->heads, a->dim, a->vdim), B200_ERR_UNSUPPORTED,
                 "b200_op_mlstm_scan: dim <= 512, heads and sequences <= 65535, gate_cap > 0");
     if (a->n_seq == 0) return B200_OK;
-    const dim3 grid((unsigned)((a->vdim + ML_COLS - 1) / ML_COLS), (unsigned)a->heads, (unsigned)a->n_seq);
     const cudaStream_t st = (cudaStream_t)stream;
     const int dpl = (a->dim + 31) / 32;
-    const size_t smem = ((size_t)2 * ML_CHUNK * a->dim + ML_CHUNK * ML_COLS + 2 * ML_CHUNK + (size_t)ML_WARPS * (ML_RG * ML_NP * 32 + ML_RG * ML_NP + ML_RG)) * 4;
-#define B200_ML_LAUNCH(N)                                                                                                                     \
-    do {                                                                                                                                      \
-        if (smem > 48 * 1024) B200_CUDA_TRY(cudaFuncSetAttribute(mlstm_scan_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-        mlstm_scan_kernel<N><<<grid, ML_THREADS, smem, st>>>(*a);                                                                            \
+    // 4 columns per warp when that still gives every SM a CTA, else 2
+    const bool wide = (int64_t)((a->vdim + 31) / 32) * a->heads * a->n_seq >= 120;
+    const int cols = (wide ? 4 : 2) * ML_WARPS, np_ = (wide ? 4 : 2) + 1;
+    const dim3 grid((unsigned)((a->vdim + cols - 1) / cols), (unsigned)a->heads, (unsigned)a->n_seq);
+    const size_t smem = ((size_t)2 * ML_CHUNK * a->dim + ML_CHUNK * cols + 2 * ML_CHUNK + (size_t)ML_WARPS * (ML_RG * np_ * 32 + ML_RG * np_ + ML_RG)) * 4;
+#define B200_ML_LAUNCH2(N, C)                                                                                                                    \
+    do {                                                                                                                                         \
+        if (smem > 48 * 1024) B200_CUDA_TRY(cudaFuncSetAttribute(mlstm_scan_kernel<N, C>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        mlstm_scan_kernel<N, C><<<grid, ML_THREADS, smem, st>>>(*a);                                                                             \
+    } while (0)
+#define B200_ML_LAUNCH(N)               \
+    do {                                \
+        if (wide) B200_ML_LAUNCH2(N, 4); \
+        else B200_ML_LAUNCH2(N, 2);     \
     } while (0)
     if (dpl <= 1) B200_ML_LAUNCH(1);
     else if (dpl <= 2) B200_ML_LAUNCH(2);
     else if (dpl <= 4) B200_ML_LAUNCH(4);
     else if (dpl <= 8) B200_ML_LAUNCH(8);
     else B200_ML_LAUNCH(16);
+#undef B200_ML_LAUNCH2
 #undef B200_ML_LAUNCH
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
