@@ -246,10 +246,11 @@ def run_mlstm(q, k, v, ig, fg, ib, fb, cap, info, state, slot_stride):
     return out.to_numpy(np.float32, (T, Hh, V))
 
 
-@pytest.mark.parametrize("Hh,D,V", [(2, 16, 24), (1, 32, 64), (3, 24, 40), (2, 80, 33), (1, 160, 8)])
+@pytest.mark.parametrize("Hh,D,V", [(2, 16, 24), (1, 32, 64), (3, 24, 40), (2, 80, 33), (1, 160, 8), (4, 8, 500), (9, 40, 450)])
 def test_mlstm_scan_whole_against_steps_and_slots(Hh, D, V):
     """Two sequences in one launch (slots 2 and 0), then the same tokens one by one through the carried state, then a slot that
-    is used again by a fresh sequence."""
+    is used again by a fresh sequence.  The large shapes give enough (head, column tile) pairs for 4 state columns per warp:
+    with (4, 8, 500) two sequences in a launch take that form and one sequence the form with 2, on the same state."""
     rng = np.random.default_rng(Hh * 100 + D + V)
     lens = [9, 5]
     T = sum(lens)
@@ -273,6 +274,27 @@ def test_mlstm_scan_whole_against_steps_and_slots(Hh, D, V):
     # slot 2 again, by a new sequence
     again = run_mlstm(q[9:], k[9:], v[9:], ig[9:], fg[9:], ib, fb, cap, [(0, 5, 2, 1)], state, stride)
     assert rel(again, want[9:]) < 2e-5
+
+
+def test_mlstm_scan_column_split_changes_between_launches():
+    """A sequence starts alone (few CTAs: 2 state columns per warp), goes on beside a new one (4 per warp), then alone again:
+    the state that one form leaves is the state the other reads."""
+    rng = np.random.default_rng(77)
+    Hh, D, V, na, nb = 4, 8, 500, 8, 4
+    T = na + nb
+    q, k, v = rng.standard_normal((T, Hh, D)), rng.standard_normal((T, Hh, D)), rng.standard_normal((T, Hh, V))
+    ig, fg = rng.standard_normal((T, Hh)) * 3, rng.standard_normal((T, Hh)) * 3 + 1
+    ib, fb, cap = rng.standard_normal(Hh), rng.standard_normal(Hh), 9.0
+    want = np.concatenate([R.mlstm_recurrence(q[a:b] * D ** -0.5, k[a:b], v[a:b], ig[a:b] + ib, fg[a:b] + fb, cap)[0] for a, b in ((0, na), (na, T))])
+    stride = int(lib().b200_mlstm_state_floats(Hh, D, V))
+    state = H.DeviceBuffer(4 * stride * 2, zero=False)
+    check(lib().b200_memset(state.ptr, 0x7f, 4 * stride * 2, None))
+    got = np.zeros_like(want)
+    got[0:3] = run_mlstm(q[0:3], k[0:3], v[0:3], ig[0:3], fg[0:3], ib, fb, cap, [(0, 3, 1, 1)], state, stride)
+    idx = list(range(3, 6)) + list(range(na, T))
+    got[idx] = run_mlstm(q[idx], k[idx], v[idx], ig[idx], fg[idx], ib, fb, cap, [(0, 3, 1, 0), (3, nb, 0, 1)], state, stride)
+    got[6:na] = run_mlstm(q[6:na], k[6:na], v[6:na], ig[6:na], fg[6:na], ib, fb, cap, [(0, na - 6, 1, 0)], state, stride)
+    assert rel(got, want) < 2e-5
 
 
 def test_mlstm_gates_saturate_without_overflow():
