@@ -25,6 +25,7 @@ enum b200_binary_op { B200_BIN_ADD = 0, B200_BIN_SUB = 1, B200_BIN_MUL = 2, B200
 enum b200_unary_op {
     B200_UN_SILU = 0, B200_UN_GELU = 1, B200_UN_GELU_QUICK = 2, B200_UN_RELU = 3, B200_UN_TANH = 4, B200_UN_SIGMOID = 5,
     B200_UN_SQR = 6, B200_UN_SCALE = 7 /* p0 = factor */, B200_UN_CLAMP = 8 /* p0 = min, p1 = max */,
+    B200_UN_SOFTCAP = 9 /* p0 * tanh(x / p0) */,
 };
 
 /* RMS_NORM (+ optional fused MUL by a per-column weight): y = x / sqrt(mean(x^2) + eps) [* w]
@@ -110,7 +111,7 @@ B200_API int b200_op_mul_mat_float(const b200_tensor *w, const b200_tensor *x, c
  * Everything here is computed in f32. */
 #define B200_EXT_TAG 0xB200E7A5u
 enum b200_ext_op {
-    B200_EXT_NORM = 1,         /* src: x, w, [gate, gate_bias, res]; op_params: [2] kind, [3] eps, [4] w_period */
+    B200_EXT_NORM = 1,         /* src: x, w, [gate, gate_bias, res, bias]; op_params: [2] kind, [3] eps, [4] w_period, [5] gate on the output */
     B200_EXT_POLYNORM = 2,     /* src: x, coef[4]; op_params: [3] eps */
     B200_EXT_ROPE_TABLE = 3,   /* src: x, pos, freqs; in place; op_params: [2] n_dims, [3] mscale, [4] neox */
     B200_EXT_WEIGHTED_SUM = 4, /* src: xs [n, J], w [J] */
@@ -118,6 +119,17 @@ enum b200_ext_op {
     B200_EXT_LATENT_KV_STORE = 6, /* src: dkv, norm w, pos, freqs, cells, cache; op_params: [2] kv_rank, [3] eps, [4] mscale, [5] n_dims */
     B200_EXT_LATENT_ATTN = 7,  /* src: q_lat, q_rot, cache, sink, tok_seq, tok_pos, cell_seq, cell_pos; op_params: [2] kv_rank, [3] scale, [4] window */
     B200_EXT_MLSTM_SCAN = 8,   /* src: q, k, v, ig, fg, i_bias, f_bias, seq_info, state; op_params: [2] heads, [3] dim, [4] vdim, [5] gate_cap */
+    B200_EXT_QKV_STORE = 9,    /* src: q, k, v, vecs (the present ones of q.b, k.b, v.b, q.norm, k.norm packed in one tensor, or NULL), pos, freqs,
+                                  cells, k cache, v cache; q in place; op_params: [2] dim, [3] vdim, [4] n_dims, [5] eps, [6] biases present, [7] norms present */
+    B200_EXT_SINK_ATTN = 10,   /* src: q, k cache, v cache, sink, tok_seq, tok_pos, cell_seq, cell_pos; op_params: [2] dim, [3] scale, [4] window,
+                                  [5] keep_first, [6] bf16 products, [7] vdim */
+    B200_EXT_LINEAR_ATTN_SCAN = 11, /* src: q, k, v, decay, seq_info, state; op_params: [2] heads, [3] dim, [4] vdim, [5] silu on q / k / v */
+    B200_EXT_MOE_ROUTE = 12,   /* src: logits, correction; dst [2 n_used, T]: per token n_used weights (f32), then n_used expert ids (i32);
+                                  op_params: [2] n_group, [3] n_group_used, [4] scale, [5] n_used */
+    B200_EXT_SILU_MUL = 13,    /* src: a, b: dst = silu(a) * b, any strides */
+    B200_EXT_MOE_COMBINE = 14, /* src: y [n, n_used, T], weights [n_used, T], add0, add1 (optional [n, T]): dst = add0 + add1 + sum_k w_k y_k */
+    B200_EXT_UNARY = 15,       /* src: x; op_params: [2] enum b200_unary_op, [3] p0, [4] p1 */
+    B200_EXT_MUL_MAT_ID = 16,  /* src: experts [K, M, E] f32 / bf16, b [K, n_b_rows, T], ids [n_used, T]: dense-weight form of MUL_MAT_ID */
 };
 
 enum b200_norm_kind { B200_NORM_LAYER = 0 /* (x - mean) / sqrt(var + eps) */, B200_NORM_RMS = 1 /* x / sqrt(mean(x^2) + eps) */ };
@@ -127,6 +139,11 @@ enum b200_norm_kind { B200_NORM_LAYER = 0 /* (x - mean) / sqrt(var + eps) */, B2
  * gate_bias: [ne0] or NULL.  One block per row, statistics in f32 (variance = mean of squared deviations, two passes). */
 B200_API int b200_op_norm(const b200_tensor *x, const float *w, int64_t w_period, const b200_tensor *gate, const float *gate_bias,
                           const b200_tensor *res, const b200_tensor *dst, float eps, int kind, b200_stream_t stream);
+
+/* The same with a bias behind the weight (dst = res + N(..) * w + bias) and the gate either in front of the norm (gate_on_output
+ * == 0, as above) or behind it: dst = res + (N(x) * w + bias) * sigmoid(gate + gate_bias). */
+B200_API int b200_op_norm_affine(const b200_tensor *x, const float *w, int64_t w_period, const float *bias, const b200_tensor *gate, const float *gate_bias,
+                                 int gate_on_output, const b200_tensor *res, const b200_tensor *dst, float eps, int kind, b200_stream_t stream);
 
 /* PolyNorm: dst = c0 N(x) + c1 N(x^2) + c2 N(x^3) + c3 with N(z) = z / sqrt(mean(z^2) + eps) over ne0, powers element by
  * element; coef: 4 floats on the device. */
@@ -188,6 +205,77 @@ typedef struct {
     float gate_cap, q_scale;
 } b200_mlstm_args;
 B200_API int b200_op_mlstm_scan(const b200_mlstm_args *a, b200_stream_t stream);
+
+
+/* dst = silu(a) * b; a, b, dst f32 of one shape with any strides (the two halves of a fused gate / up product are fine). */
+B200_API int b200_op_silu_mul_strided(const b200_tensor *a, const b200_tensor *b, const b200_tensor *dst, b200_stream_t stream);
+
+/* Softmax attention of n_head query heads over cached keys and values of n_head_kv heads (query head h reads kv head
+ * h / (n_head / n_head_kv)); one cache row per cell holds all kv heads of a token: k rows [n_head_kv * dim], v rows
+ * [n_head_kv * vdim], f32.
+ * store: per token t, q (and k) += bias; q, k <- RMS norm over the whole row * weight (when given); the first n_dims values of
+ * every head of q and k are rotated as interleaved pairs by pos[t] * freqs[i]; q is written back in place, k and v (+ bias) go
+ * to row cells[t] of the caches.  Strides in floats. */
+typedef struct {
+    float *q; int64_t q_stride;            /* [n_tokens][n_head * dim], rotated in place */
+    const float *k; int64_t k_stride;      /* [n_tokens][n_head_kv * dim] */
+    const float *v; int64_t v_stride;      /* [n_tokens][n_head_kv * vdim] */
+    const float *q_bias, *k_bias, *v_bias; /* NULL: none */
+    const float *q_norm, *k_norm;          /* NULL: no norm */
+    const int32_t *pos, *cells;
+    const float *freqs;                    /* [n_dims / 2] */
+    float *k_cache; int64_t k_cache_stride;
+    float *v_cache; int64_t v_cache_stride;
+    int32_t n_head, n_head_kv, dim, vdim, n_dims, n_tokens;
+    float eps;
+} b200_qkv_store_args;
+B200_API int b200_op_qkv_store(const b200_qkv_store_args *a, b200_stream_t stream);
+
+/* score = scale * q . k; a token sees the cells of its own sequence with cell_pos <= tok_pos and (window == 0 or
+ * tok_pos - cell_pos < window or cell_pos < keep_first); softmax in f32 whose denominator also holds exp(sink[h]) when sink !=
+ * NULL (the sink has no key and no value).  dst [n_tokens][n_head * vdim].  bf16_products as for b200_op_latent_attn. */
+typedef struct {
+    const float *q; int64_t q_stride;
+    const float *k_cache; int64_t k_cache_stride;
+    const float *v_cache; int64_t v_cache_stride;
+    const int32_t *cell_seq, *cell_pos, *tok_seq, *tok_pos;
+    const float *sink;
+    float *dst; int64_t dst_stride;
+    int32_t n_head, n_head_kv, dim, vdim, n_tokens, n_kv, window, keep_first;
+    float scale;
+    int32_t bf16_products;
+} b200_sink_attn_args;
+B200_API int b200_op_sink_attn(const b200_sink_attn_args *a, b200_stream_t stream);
+
+/* Linear attention with a decayed state per (slot, head), f32: S' = decay[h] S + k v^T, o = S'^T q, over the tokens of n_seq
+ * sequences; act != 0 applies silu to q, k and v first.  seq_info as for b200_op_mlstm_scan.  State [head][vdim][dim] per slot.
+ * q, k: [n_tokens][heads * dim], v and dst: [n_tokens][heads * vdim]; strides in floats. */
+typedef struct {
+    const float *q, *k, *v; int64_t q_stride, k_stride, v_stride;
+    const float *decay;                    /* [heads] */
+    const int32_t *seq_info; int32_t n_seq;
+    float *state; int64_t slot_stride;
+    float *dst; int64_t dst_stride;
+    int32_t heads, dim, vdim, act;
+} b200_linear_attn_args;
+B200_API int b200_op_linear_attn_scan(const b200_linear_attn_args *a, b200_stream_t stream);
+
+/* Router with sigmoid scores, a choice bias and group-limited choice, one token per warp: s = sigmoid(logits); c = s + correction
+ * (NULL: none); with n_group > 1 the n_expert experts form n_group equal groups of neighbours, a group scores the sum of its two
+ * largest c, and only experts of the n_group_used best groups can be chosen; ids[k] = the n_used largest c (ties: lowest index);
+ * w[k] = s[ids[k]] / (sum_k s[ids[k]] + 1e-20) * scale.  n_expert <= 256, n_used <= 32.  ld_* in elements. */
+B200_API int b200_op_moe_route_grouped(const float *logits, int64_t ld_logits, const float *correction, int32_t *ids, int64_t ld_ids, float *w, int64_t ld_w,
+                                       int32_t n_expert, int32_t n_used, int32_t n_group, int32_t n_group_used, float scale, int64_t n_tok, b200_stream_t stream);
+
+/* dst[t] = add0[t] + add1[t] + sum_k w[t][k] * y[t][k]; y [n, n_used, T] f32, w [n_used, T], add0 / add1 / dst [n, T] (add0, add1
+ * optional); strides in floats. */
+B200_API int b200_op_moe_combine(const float *y, int64_t y_s_slot, int64_t y_s_tok, const float *w, int64_t w_s_tok, const float *add0, int64_t add0_stride,
+                                 const float *add1, int64_t add1_stride, float *dst, int64_t dst_stride, int64_t n, int32_t n_used, int64_t n_tok, b200_stream_t stream);
+
+/* MUL_MAT_ID over dense f32 or bf16 expert matrices: as [K, M, n_expert], b [K, n_b_rows, T] f32, ids [n_used, T]:
+ * dst[:, s, t] = as[:, :, ids[s, t]] . b[:, s % n_b_rows, t].  Any K and M; f32 accumulation; products in f32 (bf16 weights are
+ * widened).  The batched tensor-core form for bf16 weights is b200_mul_mat_id_q (b200_ggml.h). */
+B200_API int b200_op_mul_mat_id_float(const b200_tensor *as, const b200_tensor *b, const b200_tensor *ids, const b200_tensor *dst, b200_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -42,11 +42,17 @@ typedef struct {
      * read n_embd, n_layer, n_vocab, n_ctx (cache cells, a multiple of 256), rms_eps (the eps of every norm) and main_device. */
     int32_t arch;
     int32_t n_seq_max;               /* sequences (and recurrent-state slots) that can be open at a time; 0 = 1 */
+    float   logit_softcap;           /* > 0: logits = cap * tanh(logits / cap) (architectures with their own graph) */
 } b200_llama_params;
 
-enum b200_arch { B200_ARCH_LLAMA = 0, B200_ARCH_GENESUN = 1 };
-enum b200_mixer { B200_MIXER_LATENT_ATTENTION = 1, B200_MIXER_MLSTM = 2 };
-enum b200_mlp { B200_MLP_NONE = 0, B200_MLP_DENSE_POLYNORM = 1 };
+enum b200_arch { B200_ARCH_LLAMA = 0, B200_ARCH_GENESUN = 1, B200_ARCH_GALIRAX = 2 };
+enum b200_mixer {
+    B200_MIXER_LATENT_ATTENTION = 1, B200_MIXER_MLSTM = 2,
+    B200_MIXER_ATTENTION = 3, /* softmax attention of heads over kv_heads cached keys / values, per-head sink, optional window */
+    B200_MIXER_LIGHTNING = 4, /* linear attention: a decayed outer-product state per head */
+};
+enum b200_mlp { B200_MLP_NONE = 0, B200_MLP_DENSE_POLYNORM = 1, B200_MLP_MOE_GATED = 2 /* routed gated experts */ };
+enum b200_rope_scaling { B200_ROPE_SCALING_NONE = 0, B200_ROPE_SCALING_YARN = 1, B200_ROPE_SCALING_BANDS = 2 /* per wavelength band */ };
 
 /* One layer of an architecture with per-layer shapes (Genesun: config.json "layers"). */
 typedef struct {
@@ -62,7 +68,21 @@ typedef struct {
     float   yarn_fast, yarn_slow;
     int32_t yarn_original;
     float   gate_cap;                /* mLSTM: soft cap of the gate pre-activations */
-    int32_t mlp, ff;                 /* enum b200_mlp and its hidden size */
+    int32_t mlp, ff;                 /* enum b200_mlp and its hidden size (per expert for B200_MLP_MOE_GATED) */
+    /* B200_MIXER_ATTENTION */
+    int32_t kv_heads;                /* key / value heads; query head h reads kv head h / (heads / kv_heads) */
+    int32_t keep_first;              /* with a window: positions below this stay visible whatever the distance */
+    int32_t qkv_bias;                /* 1: q, k, v have biases ("<leaf>.b") */
+    int32_t qk_norm;                 /* 1: RMS norm over the whole q (and k) projection with weights "q.norm" / "k.norm", before rotation */
+    int32_t rope_scaling;            /* enum b200_rope_scaling; BANDS: wavelengths below original / band_high keep their frequency,
+                                        above original / band_low are divided by yarn_factor, between the two blended linearly in
+                                        original / wavelength (yarn_factor, yarn_original give factor and original) */
+    float   band_low, band_high;
+    /* B200_MLP_MOE_GATED: n_expert experts silu(gate x) * (up x) -> down, n_expert_used per token.  Router: s = sigmoid(W x);
+     * choice by s + correction, limited to the n_group_used best of n_group equal groups of neighbouring experts (a group scores
+     * the sum of its two largest choice scores); weights s / sum(s over the chosen) * router_scale. */
+    int32_t n_expert, n_expert_used, n_group, n_group_used;
+    float   router_scale;
 } b200_layer_params;
 
 
@@ -85,6 +105,10 @@ B200_API int b200_llama_finalize(b200_llama *m, int32_t max_batch);
 
 /* Per-layer hyper-parameters (architectures other than llama), before any b200_llama_set_tensor. */
 B200_API int b200_llama_set_layer(b200_llama *m, int32_t il, const b200_layer_params *lp);
+
+/* The order in which the layers run: order[r] is the layer (weights) of run r; a layer may run several times, and every run has
+ * its own cache rows or recurrent state.  Default: every layer once, in index order.  Before any b200_llama_set_tensor. */
+B200_API int b200_llama_set_layer_order(b200_llama *m, const int32_t *order, int32_t n_runs);
 
 /* Sequences: a batch step names the sequence of every token; the decoder keeps each sequence's cache cells, positions and
  * recurrent state.  open returns a free sequence id (B200_ERR_NOMEM when n_seq_max are open); close gives its cells and its

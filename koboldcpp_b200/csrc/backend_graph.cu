@@ -723,7 +723,7 @@ static void ensure_workspaces(GraphExec *g, const ggml_cgraph *cg, int n_slots) 
     for (int i = 0; i < cg->n_nodes; i++) {
         const ggml_tensor *t = cg->nodes[i];
         if (t->op == GGML_OP_FLASH_ATTN_EXT) { const size_t b = node_fa_workspace(t); if (b > fa) fa = b; }
-        if (t->op == GGML_OP_MUL_MAT || t->op == GGML_OP_MUL_MAT_ID) { const size_t b = node_scratch_bytes(t); if (b > sc) sc = b; }
+        if (t->op == GGML_OP_MUL_MAT || t->op == GGML_OP_MUL_MAT_ID || t->op == GGML_OP_MAP_CUSTOM1) { const size_t b = node_scratch_bytes(t); if (b > sc) sc = b; }
     }
     // growing a workspace moves it: every captured graph has the old pointer baked in
     if (fa > g->fa_ws_bytes) {

@@ -50,7 +50,7 @@ static bool ext_op_supported(const ggml_tensor *op) {
     switch (op->op_params[1]) {
         case B200_EXT_NORM:
             return f32_rows(s[0]) && f32_rows(op) && same_shape(s[0], op) && (!s[1] || f32_vec(s[1])) && (!s[2] || (f32_rows(s[2]) && same_shape(s[2], op))) &&
-                   (!s[3] || f32_vec(s[3])) && (!s[4] || (f32_rows(s[4]) && same_shape(s[4], op)));
+                   (!s[3] || f32_vec(s[3])) && (!s[4] || (f32_rows(s[4]) && same_shape(s[4], op))) && (!s[5] || (f32_vec(s[5]) && s[5]->ne[0] == op->ne[0]));
         case B200_EXT_POLYNORM:
             return f32_rows(s[0]) && f32_rows(op) && same_shape(s[0], op) && f32_vec(s[1]) && nelements(s[1]) == 4;
         case B200_EXT_ROPE_TABLE:
@@ -69,9 +69,37 @@ static bool ext_op_supported(const ggml_tensor *op) {
         case B200_EXT_MLSTM_SCAN:
             for (int i = 0; i < 5; i++) if (!f32_rows(s[i])) return false;
             return (!s[5] || f32_vec(s[5])) && (!s[6] || f32_vec(s[6])) && i32_vec(s[7]) && f32_rows(s[8]) && f32_rows(op) && op->op_params[3] <= 512;
+        case B200_EXT_QKV_STORE:
+            return f32_rows(s[0]) && f32_rows(s[1]) && f32_rows(s[2]) && (!s[3] || f32_vec(s[3])) && i32_vec(s[4]) && f32_vec(s[5]) && i32_vec(s[6]) && f32_rows(s[7]) &&
+                   f32_rows(s[8]) && op->op_params[2] > 0 && op->op_params[3] > 0 && s[0]->ne[0] % op->op_params[2] == 0 && s[1]->ne[0] % op->op_params[2] == 0 &&
+                   s[2]->ne[0] % op->op_params[3] == 0 && s[1]->ne[0] / op->op_params[2] == s[2]->ne[0] / op->op_params[3];
+        case B200_EXT_SINK_ATTN:
+            return f32_rows(s[0]) && f32_rows(s[1]) && f32_rows(s[2]) && (!s[3] || f32_vec(s[3])) && i32_vec(s[4]) && i32_vec(s[5]) && i32_vec(s[6]) && i32_vec(s[7]) &&
+                   f32_rows(op) && op->op_params[2] > 0 && op->op_params[2] <= 256 && op->op_params[7] > 0 && op->op_params[7] <= 256 && s[0]->ne[0] % op->op_params[2] == 0;
+        case B200_EXT_LINEAR_ATTN_SCAN:
+            return f32_rows(s[0]) && f32_rows(s[1]) && f32_rows(s[2]) && f32_vec(s[3]) && i32_vec(s[4]) && f32_rows(s[5]) && f32_rows(op) && op->op_params[3] <= 256;
+        case B200_EXT_MOE_ROUTE:
+            return f32_rows(s[0]) && (!s[1] || f32_vec(s[1])) && f32_rows(op) && s[0]->ne[0] <= 256 && op->op_params[5] > 0 && op->op_params[5] <= 32 && op->ne[0] == 2 * op->op_params[5] &&
+                   op->ne[1] == s[0]->ne[1];
+        case B200_EXT_SILU_MUL:
+            return s[0] && s[1] && s[0]->type == GGML_TYPE_F32 && s[1]->type == GGML_TYPE_F32 && op->type == GGML_TYPE_F32 && same_shape(s[0], op) && same_shape(s[1], op);
+        case B200_EXT_MOE_COMBINE:
+            return f32_rows(s[0]) && f32_rows(s[1]) && (!s[2] || f32_rows(s[2])) && (!s[3] || f32_rows(s[3])) && f32_rows(op) && s[0]->nb[1] == 4 * (size_t)s[0]->ne[0];
+        case B200_EXT_UNARY:
+            return s[0] && s[0]->type == GGML_TYPE_F32 && op->type == GGML_TYPE_F32 && is_contiguous(s[0]) && is_contiguous(op);
+        case B200_EXT_MUL_MAT_ID:
+            return s[0] && s[1] && s[2] && (s[0]->type == GGML_TYPE_F32 || s[0]->type == GGML_TYPE_BF16) && f32_rows(s[1]) && s[2]->type == GGML_TYPE_I32 && f32_rows(op);
         default:
             return false;
     }
+}
+
+// the batched tensor-core form of an expert product over bf16 weights (the grouped GEMM of the quantised types)
+static bool ext_mul_mat_id_gemm_ok(const ggml_tensor *n) {
+    const ggml_tensor *as = n->src[0], *b = n->src[1], *ids = n->src[2];
+    if (!as || !b || !ids || as->type != GGML_TYPE_BF16 || ids->ne[0] * ids->ne[1] <= 64) return false;
+    if (as->ne[0] % 64 || as->ne[2] > 256 || ids->ne[0] * ids->ne[1] > 65535 || (((uintptr_t)as->data | as->nb[1] | as->nb[2] | (uintptr_t)b->data | b->nb[1] | b->nb[2]) & 15)) return false;
+    return b->ne[1] == 1 || b->ne[1] == ids->ne[0];
 }
 
 static void run_ext(ExecCtx &x, const ggml_tensor *n) {
@@ -81,8 +109,8 @@ static void run_ext(ExecCtx &x, const ggml_tensor *n) {
             b200_tensor a = as_b200(s[0]), d = as_b200(n), g, r;
             if (s[2]) g = as_b200(s[2]);
             if (s[4]) r = as_b200(s[4]);
-            B200_CHECK_RC(b200_op_norm(&a, s[1] ? (const float *)s[1]->data : nullptr, n->op_params[4], s[2] ? &g : nullptr, s[3] ? (const float *)s[3]->data : nullptr,
-                                       s[4] ? &r : nullptr, &d, ext_f(n, 3), n->op_params[2], x.stream));
+            B200_CHECK_RC(b200_op_norm_affine(&a, s[1] ? (const float *)s[1]->data : nullptr, n->op_params[4], s[5] ? (const float *)s[5]->data : nullptr, s[2] ? &g : nullptr,
+                                              s[3] ? (const float *)s[3]->data : nullptr, n->op_params[5], s[4] ? &r : nullptr, &d, ext_f(n, 3), n->op_params[2], x.stream));
             break;
         }
         case B200_EXT_POLYNORM: {
@@ -141,6 +169,88 @@ static void run_ext(ExecCtx &x, const ggml_tensor *n) {
             a.dst = (float *)n->data; a.dst_stride = (int64_t)(n->nb[1] / 4);
             a.heads = n->op_params[2]; a.dim = n->op_params[3]; a.vdim = n->op_params[4]; a.gate_cap = ext_f(n, 5); a.q_scale = ext_f(n, 6);
             B200_CHECK_RC(b200_op_mlstm_scan(&a, x.stream));
+            break;
+        }
+        case B200_EXT_QKV_STORE: {
+            // q [heads * dim, T] (rewritten in place: n aliases it), k [kv_heads * dim, T], v [kv_heads * vdim, T]; vecs: the present ones of
+            // q.b, k.b, v.b (op_params[6]) and q.norm, k.norm (op_params[7]), in that order
+            b200_qkv_store_args a;
+            memset(&a, 0, sizeof(a));
+            a.dim = n->op_params[2]; a.vdim = n->op_params[3]; a.n_dims = n->op_params[4]; a.eps = ext_f(n, 5);
+            a.n_head = (int32_t)(s[0]->ne[0] / a.dim); a.n_head_kv = (int32_t)(s[1]->ne[0] / a.dim); a.n_tokens = (int32_t)s[0]->ne[1];
+            a.q = (float *)s[0]->data; a.q_stride = (int64_t)(s[0]->nb[1] / 4);
+            a.k = (const float *)s[1]->data; a.k_stride = (int64_t)(s[1]->nb[1] / 4);
+            a.v = (const float *)s[2]->data; a.v_stride = (int64_t)(s[2]->nb[1] / 4);
+            const float *vec = s[3] ? (const float *)s[3]->data : nullptr;
+            const int64_t nq = (int64_t)a.n_head * a.dim, nk = (int64_t)a.n_head_kv * a.dim, nv = (int64_t)a.n_head_kv * a.vdim;
+            if (vec && n->op_params[6]) { a.q_bias = vec; a.k_bias = vec + nq; a.v_bias = vec + nq + nk; vec += nq + nk + nv; }
+            if (vec && n->op_params[7]) { a.q_norm = vec; a.k_norm = vec + nq; }
+            a.pos = (const int32_t *)s[4]->data; a.freqs = (const float *)s[5]->data; a.cells = (const int32_t *)s[6]->data;
+            a.k_cache = (float *)s[7]->data; a.k_cache_stride = (int64_t)(s[7]->nb[1] / 4);
+            a.v_cache = (float *)s[8]->data; a.v_cache_stride = (int64_t)(s[8]->nb[1] / 4);
+            B200_CHECK_RC(b200_op_qkv_store(&a, x.stream));
+            break;
+        }
+        case B200_EXT_SINK_ATTN: {
+            b200_sink_attn_args a;
+            memset(&a, 0, sizeof(a));
+            a.dim = n->op_params[2]; a.vdim = n->op_params[7]; a.scale = ext_f(n, 3); a.window = n->op_params[4]; a.keep_first = n->op_params[5]; a.bf16_products = n->op_params[6];
+            a.q = (const float *)s[0]->data; a.q_stride = (int64_t)(s[0]->nb[1] / 4); a.n_head = (int32_t)(s[0]->ne[0] / a.dim); a.n_tokens = (int32_t)s[0]->ne[1];
+            a.k_cache = (const float *)s[1]->data; a.k_cache_stride = (int64_t)(s[1]->nb[1] / 4); a.n_head_kv = (int32_t)(s[1]->ne[0] / a.dim);
+            a.v_cache = (const float *)s[2]->data; a.v_cache_stride = (int64_t)(s[2]->nb[1] / 4);
+            a.sink = s[3] ? (const float *)s[3]->data : nullptr;
+            a.tok_seq = (const int32_t *)s[4]->data; a.tok_pos = (const int32_t *)s[5]->data;
+            a.cell_seq = (const int32_t *)s[6]->data; a.cell_pos = (const int32_t *)s[7]->data; a.n_kv = (int32_t)s[6]->ne[0];
+            a.dst = (float *)n->data; a.dst_stride = (int64_t)(n->nb[1] / 4);
+            B200_CHECK_RC(b200_op_sink_attn(&a, x.stream));
+            break;
+        }
+        case B200_EXT_LINEAR_ATTN_SCAN: {
+            b200_linear_attn_args a;
+            memset(&a, 0, sizeof(a));
+            a.q = (const float *)s[0]->data; a.q_stride = (int64_t)(s[0]->nb[1] / 4);
+            a.k = (const float *)s[1]->data; a.k_stride = (int64_t)(s[1]->nb[1] / 4);
+            a.v = (const float *)s[2]->data; a.v_stride = (int64_t)(s[2]->nb[1] / 4);
+            a.decay = (const float *)s[3]->data;
+            a.seq_info = (const int32_t *)s[4]->data; a.n_seq = (int32_t)s[4]->ne[0];
+            a.state = (float *)s[5]->data; a.slot_stride = (int64_t)(s[5]->nb[1] / 4);
+            a.dst = (float *)n->data; a.dst_stride = (int64_t)(n->nb[1] / 4);
+            a.heads = n->op_params[2]; a.dim = n->op_params[3]; a.vdim = n->op_params[4]; a.act = n->op_params[5];
+            B200_CHECK_RC(b200_op_linear_attn_scan(&a, x.stream));
+            break;
+        }
+        case B200_EXT_MOE_ROUTE:
+            // a row of the result: n_used weights, then the n_used expert ids as i32
+            B200_CHECK_RC(b200_op_moe_route_grouped((const float *)s[0]->data, (int64_t)(s[0]->nb[1] / 4), s[1] ? (const float *)s[1]->data : nullptr,
+                                                    (int32_t *)n->data + n->op_params[5], (int64_t)(n->nb[1] / 4), (float *)n->data, (int64_t)(n->nb[1] / 4), (int32_t)s[0]->ne[0],
+                                                    n->op_params[5], n->op_params[2], n->op_params[3], ext_f(n, 4), s[0]->ne[1], x.stream));
+            break;
+        case B200_EXT_SILU_MUL: {
+            b200_tensor a = as_b200(s[0]), b = as_b200(s[1]), d = as_b200(n);
+            B200_CHECK_RC(b200_op_silu_mul_strided(&a, &b, &d, x.stream));
+            break;
+        }
+        case B200_EXT_MOE_COMBINE:
+            B200_CHECK_RC(b200_op_moe_combine((const float *)s[0]->data, (int64_t)(s[0]->nb[1] / 4), (int64_t)(s[0]->nb[2] / 4), (const float *)s[1]->data, (int64_t)(s[1]->nb[1] / 4),
+                                              s[2] ? (const float *)s[2]->data : nullptr, s[2] ? (int64_t)(s[2]->nb[1] / 4) : 0, s[3] ? (const float *)s[3]->data : nullptr,
+                                              s[3] ? (int64_t)(s[3]->nb[1] / 4) : 0, (float *)n->data, (int64_t)(n->nb[1] / 4), n->ne[0], (int32_t)s[0]->ne[1], n->ne[1], x.stream));
+            break;
+        case B200_EXT_UNARY: {
+            b200_tensor a = as_b200(s[0]), d = as_b200(n);
+            B200_CHECK_RC(b200_op_unary(n->op_params[2], &a, &d, ext_f(n, 3), ext_f(n, 4), x.stream));
+            break;
+        }
+        case B200_EXT_MUL_MAT_ID: {
+            const ggml_tensor *as = s[0], *b = s[1], *ids = s[2];
+            if (ext_mul_mat_id_gemm_ok(n) && node_scratch_bytes(n) <= x.scratch_bytes) {
+                B200_CHECK_RC(b200_mul_mat_id_q(as->type, as->data, as->nb[1], as->nb[2], (int32_t)as->ne[2], (const int32_t *)ids->data, (int64_t)(ids->nb[1] / 4),
+                                                (const float *)b->data, (int64_t)(b->nb[1] / 4), (int64_t)(b->nb[2] / 4), (float *)n->data, (int64_t)(n->nb[1] / 4),
+                                                (int64_t)(n->nb[2] / 4), as->ne[0], as->ne[1], ids->ne[0], b->ne[1], ids->ne[1], x.scratch, x.scratch_bytes, x.stream));
+                x.launches += 2;
+                break;
+            }
+            b200_tensor ta = as_b200(as), tb = as_b200(b), ti = as_b200(ids), td = as_b200(n);
+            B200_CHECK_RC(b200_op_mul_mat_id_float(&ta, &tb, &ti, &td, x.stream));
             break;
         }
         default:
@@ -475,6 +585,8 @@ size_t node_scratch_bytes(const ggml_tensor *n) {
         const size_t one = b200_mul_mat_q_workspace_bytes(w->type, w->ne[0], w->ne[1], a->ne[1]);
         return (a->ne[2] > 1 && a->ne[3] == 1 && w->ne[2] == a->ne[2]) ? one * (size_t)a->ne[2] : one;
     }
+    if (n->op == GGML_OP_MAP_CUSTOM1 && (uint32_t)n->op_params[0] == B200_EXT_TAG && n->op_params[1] == B200_EXT_MUL_MAT_ID && ext_mul_mat_id_gemm_ok(n))
+        return b200_mul_mat_id_q_workspace_bytes(n->src[0]->type, n->src[0]->ne[0], n->src[0]->ne[1], n->src[2]->ne[0], n->src[2]->ne[1], (int32_t)n->src[0]->ne[2]);
     if (n->op == GGML_OP_MUL_MAT_ID && n->src[0] && n->src[2] && n->src[2]->ne[0] * n->src[2]->ne[1] > B200_GEMV_MAX_JOBS)
         return b200_mul_mat_id_q_workspace_bytes(n->src[0]->type, n->src[0]->ne[0], n->src[0]->ne[1], n->src[2]->ne[0], n->src[2]->ne[1], (int32_t)n->src[0]->ne[2]);
     if (n->op != GGML_OP_MUL_MAT || !n->src[0] || !n->src[1] || !is_quantized(n->src[0]->type) || n->src[1]->ne[1] <= 8) return 0;

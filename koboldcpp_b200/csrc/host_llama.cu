@@ -6,7 +6,7 @@
 // No compute happens in this file.
 #include "host_model.h"
 
-const Arch *b200::host::find_arch(int32_t id) { return id == B200_ARCH_GENESUN ? genesun_arch() : nullptr; }
+const Arch *b200::host::find_arch(int32_t id) { return id == B200_ARCH_GENESUN ? genesun_arch() : id == B200_ARCH_GALIRAX ? galirax_arch() : nullptr; }
 
 extern "C" int b200_llama_new(const b200_llama_params *p, b200_llama **out) {
     LL_REQUIRE(p && out, B200_ERR_INVALID, "b200_llama_new: NULL argument");
@@ -88,6 +88,14 @@ extern "C" int b200_llama_set_layer(b200_llama *m, int32_t il, const b200_layer_
     LL_REQUIRE(m->arch, B200_ERR_UNSUPPORTED, "b200_llama_set_layer: the llama architecture has one shape for all layers (b200_llama_params)");
     LL_REQUIRE(il >= 0 && il < m->hp.n_layer && m->weights.empty() && !m->finalized, B200_ERR_INVALID, "b200_llama_set_layer: layer %d of %d, before any tensor", il, m->hp.n_layer);
     m->layer_hp[(size_t)il] = *lp;
+    return B200_OK;
+}
+
+extern "C" int b200_llama_set_layer_order(b200_llama *m, const int32_t *order, int32_t n_runs) {
+    LL_REQUIRE(m && order && n_runs > 0, B200_ERR_INVALID, "b200_llama_set_layer_order: bad argument");
+    LL_REQUIRE(m->arch && m->weights.empty() && !m->finalized, B200_ERR_INVALID, "b200_llama_set_layer_order: for architectures with per-layer shapes, before any tensor");
+    for (int32_t r = 0; r < n_runs; r++) LL_REQUIRE(order[r] >= 0 && order[r] < m->hp.n_layer, B200_ERR_INVALID, "b200_llama_set_layer_order: run %d names layer %d of %d", r, order[r], m->hp.n_layer);
+    m->run_layer.assign(order, order + n_runs);
     return B200_OK;
 }
 

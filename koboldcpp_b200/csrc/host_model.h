@@ -261,6 +261,7 @@ struct Arch {
 };
 const Arch *find_arch(int32_t id);
 const Arch *genesun_arch();
+const Arch *galirax_arch();
 
 }  // namespace host
 }  // namespace b200
@@ -317,6 +318,7 @@ struct b200_llama {
     // sequence cache, the inputs of a batch step and the regions of the compute buffer the architecture's builder fills
     const b200::host::Arch *arch = nullptr;
     std::vector<b200_layer_params> layer_hp;
+    std::vector<int32_t> run_layer;          // the layer of every run, in execution order (empty: every layer once)
     std::shared_ptr<void> arch_data;
     b200::host::SeqCache cache;
     ggml_tensor inp_cells, inp_tok_seq, inp_cell_seq, inp_cell_pos, inp_seq_info;

@@ -1166,15 +1166,17 @@ extern "C" int b200_mul_mat_id_q(int type, const void *as, size_t w_row_bytes, s
     if (!as || !ids || !b || !dst) { set_error("b200_mul_mat_id_q: NULL argument"); return B200_ERR_INVALID; }
     if (!(type == B200_TYPE_Q4_0 || type == B200_TYPE_Q8_0 || type == B200_TYPE_Q4_K || type == B200_TYPE_Q5_K || type == B200_TYPE_Q6_K ||
           type == B200_TYPE_Q4_1 || type == B200_TYPE_Q5_0 || type == B200_TYPE_Q5_1 || type == B200_TYPE_Q2_K || type == B200_TYPE_Q3_K ||
-          type == B200_TYPE_IQ4_NL || type == B200_TYPE_IQ4_XS)) {
+          type == B200_TYPE_IQ4_NL || type == B200_TYPE_IQ4_XS || type == B200_TYPE_BF16)) {
         set_error("b200_mul_mat_id_q: unsupported weight type %d", type);
         return B200_ERR_UNSUPPORTED;
     }
-    if (K <= 0 || K % 256 || M < 0 || T < 0 || n_used < 1 || n_b_rows < 1 || n_expert < 1 || n_expert > MID_MAX_EXPERTS) {
-        set_error("b200_mul_mat_id_q: bad shape (K must be a multiple of 256, at most %d experts)", MID_MAX_EXPERTS);
-        return K % 256 ? B200_ERR_UNSUPPORTED : B200_ERR_INVALID;
+    const int64_t k_unit = type == B200_TYPE_BF16 ? MQ_BK : 256;  // dense rows step by one K tile, quantised rows by a 256-value group
+    if (K <= 0 || K % k_unit || M < 0 || T < 0 || n_used < 1 || n_b_rows < 1 || n_expert < 1 || n_expert > MID_MAX_EXPERTS) {
+        set_error("b200_mul_mat_id_q: bad shape (K must be a multiple of %d, at most %d experts)", (int)k_unit, MID_MAX_EXPERTS);
+        return K % k_unit ? B200_ERR_UNSUPPORTED : B200_ERR_INVALID;
     }
     if (M == 0 || T == 0) return B200_OK;
+    if (type == B200_TYPE_BF16 && ((w_row_bytes | expert_bytes | (uintptr_t)as) & 15)) { set_error("b200_mul_mat_id_q: bf16 rows must be 16-byte aligned"); return B200_ERR_UNSUPPORTED; }
     const int bv = type_block_values(type);
     const size_t row_bytes = (size_t)(K / bv) * type_block_bytes(type);
     if (w_row_bytes < row_bytes || ((w_row_bytes | expert_bytes | (uintptr_t)as) & 1)) { set_error("b200_mul_mat_id_q: weight stride/alignment"); return B200_ERR_INVALID; }
@@ -1221,6 +1223,7 @@ extern "C" int b200_mul_mat_id_q(int type, const void *as, size_t w_row_bytes, s
         case B200_TYPE_Q3_K: return mid_dispatch_bn<B200_TYPE_Q3_K>(p, bn, n_rows, (unsigned)max_tiles, st);
         case B200_TYPE_IQ4_NL: return mid_dispatch_bn<B200_TYPE_IQ4_NL>(p, bn, n_rows, (unsigned)max_tiles, st);
         case B200_TYPE_IQ4_XS: return mid_dispatch_bn<B200_TYPE_IQ4_XS>(p, bn, n_rows, (unsigned)max_tiles, st);
+        case B200_TYPE_BF16: return mid_dispatch_bn<B200_TYPE_BF16>(p, bn, n_rows, (unsigned)max_tiles, st);
     }
     return B200_ERR_UNSUPPORTED;
 }

@@ -174,6 +174,7 @@ __device__ __forceinline__ float unary_apply(int op, float x, float p0, float p1
         case B200_UN_SQR: return x * x;
         case B200_UN_SCALE: return x * p0;
         case B200_UN_CLAMP: return x < p0 ? p0 : (x > p1 ? p1 : x);
+        case B200_UN_SOFTCAP: return p0 * tanhf(x / p0);
     }
     return x;
 }
@@ -913,7 +914,7 @@ extern "C" int b200_op_unary(int op, const b200_tensor *x, const b200_tensor *ds
     REQUIRE(x && dst && x->data && dst->data, B200_ERR_INVALID, "b200_op_unary: NULL argument");
     REQUIRE(x->type == B200_TYPE_F32 && dst->type == B200_TYPE_F32 && contiguous(x) && contiguous(dst) && nelements(x) == nelements(dst),
             B200_ERR_UNSUPPORTED, "b200_op_unary: contiguous f32 only");
-    REQUIRE(op >= 0 && op <= B200_UN_CLAMP, B200_ERR_INVALID, "b200_op_unary: bad op %d", op);
+    REQUIRE(op >= 0 && op <= B200_UN_SOFTCAP, B200_ERR_INVALID, "b200_op_unary: bad op %d", op);
     const int64_t n = nelements(x);
     if (n == 0) return B200_OK;
     unary_kernel<<<grid1d(n, 256), 256, 0, (cudaStream_t)stream>>>(op, (const float *)x->data, (float *)dst->data, n, p0, p1);

@@ -9,8 +9,8 @@ using namespace opx;
 
 // ------------------------------------------------------------------------------------------------ norm (+ gate, + residual)
 template <int KIND, bool GATE>
-__global__ void norm_kernel(TD x, const float *__restrict__ w, int64_t w_period, TD gate, const float *__restrict__ gate_bias, TD res, bool has_res, TD dst,
-                            float eps) {
+__global__ void norm_kernel(TD x, const float *__restrict__ w, int64_t w_period, const float *__restrict__ bias, TD gate, const float *__restrict__ gate_bias,
+                            bool gate_out, TD res, bool has_res, TD dst, float eps) {
     __shared__ float sh[32];
     extern __shared__ float rowbuf[];  // the gated row (GATE only)
     const int64_t r = blockIdx.x;
@@ -23,14 +23,14 @@ __global__ void norm_kernel(TD x, const float *__restrict__ w, int64_t w_period,
     float s = 0.f;
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
         float v = xr[i];
-        if (GATE) {
+        if (GATE && !gate_out) {
             v *= sigmoidf_(gr[i] + (gate_bias ? gate_bias[i] : 0.f));
             rowbuf[i] = v;
         }
         s += KIND == B200_NORM_RMS ? v * v : v;
     }
     if (GATE) __syncthreads();
-    const float *src = GATE ? rowbuf : xr;
+    const float *src = (GATE && !gate_out) ? rowbuf : xr;
     float mean = 0.f, var;
     if (KIND == B200_NORM_RMS) {
         var = block_sum(s, sh) / (float)n;
@@ -44,6 +44,8 @@ __global__ void norm_kernel(TD x, const float *__restrict__ w, int64_t w_period,
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
         float v = (src[i] - mean) * scale;
         if (wr) v *= wr[i];
+        if (bias) v += bias[i];
+        if (GATE && gate_out) v *= sigmoidf_(gr[i] + (gate_bias ? gate_bias[i] : 0.f));
         if (rr) v += rr[i];
         yr[i] = v;
     }
@@ -74,8 +76,8 @@ __global__ void polynorm_kernel(TD x, const float *__restrict__ coef, TD dst, fl
 // Rows of up to blockDim * VPT values stay in registers: every load of the row (and of its gate) is issued before the first
 // reduction, so a row costs one memory latency for the statistics and one for the weight / residual, whatever its length.
 template <int KIND, bool GATE, int VPT>
-__global__ void __launch_bounds__(1024) norm_reg_kernel(TD x, const float *__restrict__ w, int64_t w_period, TD gate, const float *__restrict__ gate_bias, TD res, bool has_res, TD dst,
-                                float eps) {
+__global__ void __launch_bounds__(1024) norm_reg_kernel(TD x, const float *__restrict__ w, int64_t w_period, const float *__restrict__ bias, TD gate,
+                                                        const float *__restrict__ gate_bias, bool gate_out, TD res, bool has_res, TD dst, float eps) {
     __shared__ float sh[32];
     const int64_t r = blockIdx.x;
     const float *xr = (const float *)row_ptr(x, r);
@@ -96,7 +98,7 @@ __global__ void __launch_bounds__(1024) norm_reg_kernel(TD x, const float *__res
     float s = 0.f;
 #pragma unroll
     for (int k = 0; k < VPT; k++) {
-        if (GATE) v[k] *= sigmoidf_(g[k]);
+        if (GATE && !gate_out) v[k] *= sigmoidf_(g[k]);
         s += KIND == B200_NORM_RMS ? v[k] * v[k] : v[k];
     }
     float mean = 0.f, var;
@@ -113,7 +115,12 @@ __global__ void __launch_bounds__(1024) norm_reg_kernel(TD x, const float *__res
 #pragma unroll
     for (int k = 0; k < VPT; k++) {
         const int i = threadIdx.x + k * blockDim.x;
-        if (i < n) yr[i] = (v[k] - mean) * scale * wv[k] + rv[k];
+        if (i < n) {
+            float y = (v[k] - mean) * scale * wv[k];
+            if (bias) y += bias[i];
+            if (GATE && gate_out) y *= sigmoidf_(g[k]);
+            yr[i] = y + rv[k];
+        }
     }
 }
 
@@ -197,6 +204,12 @@ using namespace b200::opx;
 
 extern "C" int b200_op_norm(const b200_tensor *x, const float *w, int64_t w_period, const b200_tensor *gate, const float *gate_bias, const b200_tensor *res,
                             const b200_tensor *dst, float eps, int kind, b200_stream_t stream) {
+    return b200_op_norm_affine(x, w, w_period, nullptr, gate, gate_bias, 0, res, dst, eps, kind, stream);
+}
+
+extern "C" int b200_op_norm_affine(const b200_tensor *x, const float *w, int64_t w_period, const float *bias, const b200_tensor *gate, const float *gate_bias,
+                                   int gate_on_output, const b200_tensor *res, const b200_tensor *dst, float eps, int kind, b200_stream_t stream) {
+    const bool gate_out = gate && gate_on_output != 0;
     OPX_REQUIRE(x && dst && x->data && dst->data, B200_ERR_INVALID, "b200_op_norm: NULL argument");
     OPX_REQUIRE(x->type == B200_TYPE_F32 && dst->type == B200_TYPE_F32 && x->nb[0] == 4 && dst->nb[0] == 4 && same_shape(x, dst), B200_ERR_UNSUPPORTED,
                 "b200_op_norm: f32 rows of one shape only");
@@ -213,7 +226,7 @@ extern "C" int b200_op_norm(const b200_tensor *x, const float *w, int64_t w_peri
     if (x->ne[0] <= 16384) {  // the row fits the registers of one block
         const int n = (int)x->ne[0];
         const int rb = n <= 256 ? 64 : n <= 1024 ? 128 : n <= 2048 ? 256 : n <= 4096 ? 512 : 1024;
-#define B200_NORM_REG(K, G, V) norm_reg_kernel<K, G, V><<<(unsigned)rows, rb, 0, st>>>(td(x), w, w_period, tg, gate_bias, tr, res != nullptr, td(dst), eps)
+#define B200_NORM_REG(K, G, V) norm_reg_kernel<K, G, V><<<(unsigned)rows, rb, 0, st>>>(td(x), w, w_period, bias, tg, gate_bias, gate_out, tr, res != nullptr, td(dst), eps)
 #define B200_NORM_REG_V(K, G) do { if ((n + rb - 1) / rb <= 4) B200_NORM_REG(K, G, 4); else if ((n + rb - 1) / rb <= 8) B200_NORM_REG(K, G, 8); else B200_NORM_REG(K, G, 16); } while (0)
         if (kind == B200_NORM_RMS) { if (gate) B200_NORM_REG_V(B200_NORM_RMS, true); else B200_NORM_REG_V(B200_NORM_RMS, false); }
         else { if (gate) B200_NORM_REG_V(B200_NORM_LAYER, true); else B200_NORM_REG_V(B200_NORM_LAYER, false); }
@@ -222,11 +235,11 @@ extern "C" int b200_op_norm(const b200_tensor *x, const float *w, int64_t w_peri
         B200_CUDA_TRY(cudaGetLastError());
         return B200_OK;
     }
-    const size_t smem = gate ? (size_t)x->ne[0] * 4 : 0;
+    const size_t smem = gate && !gate_out ? (size_t)x->ne[0] * 4 : 0;
 #define B200_NORM_LAUNCH(K, G)                                                                                                                   \
     do {                                                                                                                                         \
         if (smem > 48 * 1024) B200_CUDA_TRY(cudaFuncSetAttribute(norm_kernel<K, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));    \
-        norm_kernel<K, G><<<(unsigned)rows, block, smem, st>>>(td(x), w, w_period, tg, gate_bias, tr, res != nullptr, td(dst), eps);             \
+        norm_kernel<K, G><<<(unsigned)rows, block, smem, st>>>(td(x), w, w_period, bias, tg, gate_bias, gate_out, tr, res != nullptr, td(dst), eps);             \
     } while (0)
     if (kind == B200_NORM_RMS) { if (gate) B200_NORM_LAUNCH(B200_NORM_RMS, true); else B200_NORM_LAUNCH(B200_NORM_RMS, false); }
     else { if (gate) B200_NORM_LAUNCH(B200_NORM_LAYER, true); else B200_NORM_LAUNCH(B200_NORM_LAYER, false); }

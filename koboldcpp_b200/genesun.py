@@ -92,19 +92,26 @@ def layer_params(layer: dict) -> LayerParams:
 class SequenceModel:
     """A model of an architecture with sequences, resident on one device: tensors in, batch steps out."""
 
-    def __init__(self, arch: int, width: int, vocab: int, layers: list[LayerParams], eps: float, n_ctx: int, n_seq_max: int, max_batch: int, device: int = 0):
+    def __init__(self, arch: int, width: int, vocab: int, layers: list[LayerParams], eps: float, n_ctx: int, n_seq_max: int, max_batch: int, device: int = 0,
+                 logit_softcap: float = 0.0, order: list[int] | None = None):
+        """order: the layer of every run, in execution order (None: every layer once); a layer that runs several times has a cache
+        or state per run."""
         L = _l()
         if L.ggml_backend_b200_get_device_count() <= 0:
             raise B200Error("no CUDA device: the B200 backend has no CPU fallback")
         self.width, self.vocab, self.n_layer = width, vocab, len(layers)
         self.n_ctx = (max(n_ctx, 1) + 255) // 256 * 256
         self.n_seq_max, self.max_batch = n_seq_max, max_batch
-        p = LlamaParams(n_embd=width, n_layer=len(layers), n_vocab=vocab, n_ctx=self.n_ctx, rms_eps=eps, main_device=device, arch=arch, n_seq_max=n_seq_max)
+        p = LlamaParams(n_embd=width, n_layer=len(layers), n_vocab=vocab, n_ctx=self.n_ctx, rms_eps=eps, main_device=device, arch=arch, n_seq_max=n_seq_max,
+                        logit_softcap=logit_softcap)
         h = C.c_void_p()
         check(L.b200_llama_new(C.byref(p), C.byref(h)), "b200_llama_new")
         self.h = h
         for il, lp in enumerate(layers):
             check(L.b200_llama_set_layer(self.h, il, C.byref(lp)), f"set_layer {il}")
+        if order is not None:
+            o = np.ascontiguousarray(order, dtype=np.int32)
+            check(L.b200_llama_set_layer_order(self.h, o.ctypes.data, len(o)), "set_layer_order")
         self._logits = None
 
     def set_tensor(self, name: str, ty: int, shape: tuple[int, ...], data: np.ndarray) -> None:

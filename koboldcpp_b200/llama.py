@@ -19,7 +19,7 @@ class LlamaParams(C.Structure):
                 ("type_k", C.c_int32), ("type_v", C.c_int32), ("rope_neox", C.c_int32), ("n_ctx_orig", C.c_int32),
                 ("rms_eps", C.c_float), ("rope_freq_base", C.c_float), ("rope_freq_scale", C.c_float),
                 ("main_device", C.c_int32), ("n_split_devices", C.c_int32), ("tensor_split", C.c_float * 16),
-                ("tp_rank", C.c_int32), ("tp_world", C.c_int32), ("arch", C.c_int32), ("n_seq_max", C.c_int32)]
+                ("tp_rank", C.c_int32), ("tp_world", C.c_int32), ("arch", C.c_int32), ("n_seq_max", C.c_int32), ("logit_softcap", C.c_float)]
 
 
 class LayerParams(C.Structure):
@@ -27,7 +27,10 @@ class LayerParams(C.Structure):
     _fields_ = [("mixer", C.c_int32), ("heads", C.c_int32), ("dim", C.c_int32), ("vdim", C.c_int32), ("rot_dim", C.c_int32), ("kv_rank", C.c_int32),
                 ("q_rank", C.c_int32), ("kv_from", C.c_int32), ("window", C.c_int32), ("scale", C.c_float), ("rope_dims", C.c_int32), ("rope_base", C.c_float),
                 ("yarn_factor", C.c_float), ("yarn_fast", C.c_float), ("yarn_slow", C.c_float), ("yarn_original", C.c_int32), ("gate_cap", C.c_float),
-                ("mlp", C.c_int32), ("ff", C.c_int32)]
+                ("mlp", C.c_int32), ("ff", C.c_int32),
+                ("kv_heads", C.c_int32), ("keep_first", C.c_int32), ("qkv_bias", C.c_int32), ("qk_norm", C.c_int32), ("rope_scaling", C.c_int32),
+                ("band_low", C.c_float), ("band_high", C.c_float),
+                ("n_expert", C.c_int32), ("n_expert_used", C.c_int32), ("n_group", C.c_int32), ("n_group_used", C.c_int32), ("router_scale", C.c_float)]
 
 
 _SIGS = {
@@ -44,6 +47,7 @@ _SIGS = {
     "b200_llama_replay": (C.c_int, [C.c_void_p]),
     "b200_llama_stream": (C.c_void_p, [C.c_void_p]),
     "b200_llama_set_layer": (C.c_int, [C.c_void_p, C.c_int32, C.POINTER(LayerParams)]),
+    "b200_llama_set_layer_order": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32]),
     "b200_llama_seq_open": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32)]),
     "b200_llama_seq_close": (C.c_int, [C.c_void_p, C.c_int32]),
     "b200_llama_seq_length": (C.c_int, [C.c_void_p, C.c_int32]),

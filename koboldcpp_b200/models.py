@@ -4,11 +4,12 @@ from __future__ import annotations
 import json
 from pathlib import Path
 
-from . import genesun
+from . import galirax, genesun
 from .lib import B200Error
 
 ARCHITECTURES = {
     "Genesun": genesun.load,
+    "Galirax": galirax.load,
 }
 
 
