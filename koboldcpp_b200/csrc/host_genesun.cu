@@ -163,6 +163,7 @@ int gs_finalize(b200_llama *m) {
     const b200_llama_params &hp = m->hp;
     m->arch_data = std::shared_ptr<void>(new GsData(), [](void *p) { delete (GsData *)p; });
     GsData *g = gs(m);
+    LL_REQUIRE(m->run_layer.empty(), B200_ERR_UNSUPPORTED, "b200_llama_finalize: this architecture runs every layer once, in order");
     g->layers.resize((size_t)hp.n_layer);
     g->embed = find_w(m, "embed"); g->final_norm = find_w(m, "final.norm"); g->head = find_w(m, "head");
     LL_REQUIRE(g->embed && g->final_norm && g->head, B200_ERR_INVALID, "b200_llama_finalize: embed / final.norm / head missing");

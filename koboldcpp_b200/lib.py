@@ -81,6 +81,31 @@ class MlstmArgs(C.Structure):
                 ("vdim", C.c_int32), ("gate_cap", C.c_float), ("q_scale", C.c_float)]
 
 
+class QkvStoreArgs(C.Structure):
+    """b200_qkv_store_args (include/b200_ggml_ops.h); strides in floats."""
+    _fields_ = [("q", C.c_void_p), ("q_stride", C.c_int64), ("k", C.c_void_p), ("k_stride", C.c_int64), ("v", C.c_void_p), ("v_stride", C.c_int64),
+                ("q_bias", C.c_void_p), ("k_bias", C.c_void_p), ("v_bias", C.c_void_p), ("q_norm", C.c_void_p), ("k_norm", C.c_void_p),
+                ("pos", C.c_void_p), ("cells", C.c_void_p), ("freqs", C.c_void_p), ("k_cache", C.c_void_p), ("k_cache_stride", C.c_int64),
+                ("v_cache", C.c_void_p), ("v_cache_stride", C.c_int64), ("n_head", C.c_int32), ("n_head_kv", C.c_int32), ("dim", C.c_int32),
+                ("vdim", C.c_int32), ("n_dims", C.c_int32), ("n_tokens", C.c_int32), ("eps", C.c_float)]
+
+
+class SinkAttnArgs(C.Structure):
+    """b200_sink_attn_args (include/b200_ggml_ops.h); strides in floats."""
+    _fields_ = [("q", C.c_void_p), ("q_stride", C.c_int64), ("k_cache", C.c_void_p), ("k_cache_stride", C.c_int64), ("v_cache", C.c_void_p),
+                ("v_cache_stride", C.c_int64), ("cell_seq", C.c_void_p), ("cell_pos", C.c_void_p), ("tok_seq", C.c_void_p), ("tok_pos", C.c_void_p),
+                ("sink", C.c_void_p), ("dst", C.c_void_p), ("dst_stride", C.c_int64), ("n_head", C.c_int32), ("n_head_kv", C.c_int32), ("dim", C.c_int32),
+                ("vdim", C.c_int32), ("n_tokens", C.c_int32), ("n_kv", C.c_int32), ("window", C.c_int32), ("keep_first", C.c_int32), ("scale", C.c_float),
+                ("bf16_products", C.c_int32)]
+
+
+class LinearAttnArgs(C.Structure):
+    """b200_linear_attn_args (include/b200_ggml_ops.h); strides in floats."""
+    _fields_ = [("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("q_stride", C.c_int64), ("k_stride", C.c_int64), ("v_stride", C.c_int64),
+                ("decay", C.c_void_p), ("seq_info", C.c_void_p), ("n_seq", C.c_int32), ("state", C.c_void_p), ("slot_stride", C.c_int64),
+                ("dst", C.c_void_p), ("dst_stride", C.c_int64), ("heads", C.c_int32), ("dim", C.c_int32), ("vdim", C.c_int32), ("act", C.c_int32)]
+
+
 _SIGS = {
     # name: (restype, argtypes)
     "b200_last_error": (C.c_char_p, []),
@@ -150,6 +175,18 @@ _OPS_SIGS = {
     "b200_op_mlstm_scan": (C.c_int, [C.POINTER(MlstmArgs), C.c_void_p]),
     "b200_op_mul_mat_float": (C.c_int, [C.POINTER(Tensor), C.POINTER(Tensor), C.POINTER(Tensor), C.c_void_p]),
     "b200_op_rms_norm_mul": (C.c_int, [C.POINTER(Tensor), C.c_void_p, C.c_void_p, C.POINTER(Tensor), C.c_float, C.c_void_p]),
+    "b200_op_unary": (C.c_int, [C.c_int, C.POINTER(Tensor), C.POINTER(Tensor), C.c_float, C.c_float, C.c_void_p]),
+    "b200_op_norm_affine": (C.c_int, [C.POINTER(Tensor), C.c_void_p, C.c_int64, C.c_void_p, C.POINTER(Tensor), C.c_void_p, C.c_int, C.POINTER(Tensor), C.POINTER(Tensor),
+                                      C.c_float, C.c_int, C.c_void_p]),
+    "b200_op_silu_mul_strided": (C.c_int, [C.POINTER(Tensor), C.POINTER(Tensor), C.POINTER(Tensor), C.c_void_p]),
+    "b200_op_qkv_store": (C.c_int, [C.POINTER(QkvStoreArgs), C.c_void_p]),
+    "b200_op_sink_attn": (C.c_int, [C.POINTER(SinkAttnArgs), C.c_void_p]),
+    "b200_op_linear_attn_scan": (C.c_int, [C.POINTER(LinearAttnArgs), C.c_void_p]),
+    "b200_op_moe_route_grouped": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                            C.c_float, C.c_int64, C.c_void_p]),
+    "b200_op_moe_combine": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
+                                      C.c_int64, C.c_int32, C.c_int64, C.c_void_p]),
+    "b200_op_mul_mat_id_float": (C.c_int, [C.POINTER(Tensor), C.POINTER(Tensor), C.POINTER(Tensor), C.POINTER(Tensor), C.c_void_p]),
 }
 
 _lib = None
