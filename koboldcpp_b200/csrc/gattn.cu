@@ -176,6 +176,213 @@ static int launch_sink_attn(const b200_sink_attn_args *a, cudaStream_t st) {
     return launch_sink_attn2<ND, 8>(a, st);
 }
 
+// ------------------------------------------------------------------------------------------------ attention, bf16 products (prompts)
+// The tensor cores take both contractions (mma.sync.m16n8k16, bf16 in, f32 accumulators).  One CTA per (GM_TOK consecutive tokens
+// of the batch, head), a warp per 16 tokens: its query rows stay in registers as A fragments for the whole pass, the scores of a
+// tile of GM_CELLS cells stay in accumulator registers through scale, visibility and the online softmax (all f32), and are
+// repacked in place as the A fragments of the second product, so a warp never exchanges anything with another warp.  Keys and
+// values of a tile are converted to bf16 on the way into shared memory (free cells are read as zeros: zero weight times whatever
+// an unwritten row holds must not reach the sum).  Before a tile is loaded every warp tests its 16 tokens against the tile's 32
+// cells (a lane per cell): a tile nobody sees is skipped by the CTA, and a warp whose rows see nothing in it skips the products.
+// KS = ceil(dim / 16), VS = ceil(vdim / 16): head sizes are padded with zeros in shared memory, so any size up to 128 runs.
+constexpr int GM_TOK = 64, GM_CELLS = 32, GM_WARPS = 4;
+__device__ __forceinline__ void gm_ldsm4(unsigned addr, unsigned &r0, unsigned &r1, unsigned &r2, unsigned &r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void gm_ldsm4_t(unsigned addr, unsigned &r0, unsigned &r1, unsigned &r2, unsigned &r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void gm_mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned gm_pack_bf2(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const unsigned *>(&v);
+}
+// rows [r0, r0 + n_rows) of an f32 matrix -> bf16 rows of `stride` bytes in shared memory, `width` values kept, the rest of the
+// padded row (pad values) zero; row_of(i) gives the source row or nullptr (a row of zeros)
+template <typename RowOf>
+__device__ __forceinline__ void gm_stage(unsigned char *dst, int stride, int n_rows, int width, int pad, bool vec4, RowOf row_of) {
+    const int per = pad / 4;  // groups of 4 values per row
+    for (int idx = threadIdx.x; idx < n_rows * per; idx += GM_WARPS * 32) {
+        const int r = idx / per, j = (idx - r * per) * 4;
+        const float *src = row_of(r);
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (src) {
+            if (vec4 && j + 3 < width) v = *reinterpret_cast<const float4 *>(src + j);
+            else {
+                if (j < width) v.x = src[j];
+                if (j + 1 < width) v.y = src[j + 1];
+                if (j + 2 < width) v.z = src[j + 2];
+                if (j + 3 < width) v.w = src[j + 3];
+            }
+        }
+        *reinterpret_cast<uint2 *>(dst + r * stride + j * 2) = make_uint2(gm_pack_bf2(v.x, v.y), gm_pack_bf2(v.z, v.w));
+    }
+}
+
+template <int KS, int VS>
+__global__ void __launch_bounds__(GM_WARPS * 32) sink_attn_mma_kernel(const b200_sink_attn_args a) {
+    constexpr int QSTRIDE = KS * 32 + 16, VSTRIDE = VS * 32 + 16;  // bytes per bf16 row: 8 consecutive rows start in 8 different 16-byte bank groups
+    __shared__ __align__(16) unsigned char qs[GM_TOK * QSTRIDE];
+    __shared__ __align__(16) unsigned char ks[GM_CELLS * QSTRIDE];
+    __shared__ __align__(16) unsigned char vs[GM_CELLS * VSTRIDE];
+    __shared__ int cseq[GM_CELLS], cpos[GM_CELLS];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+    const int t0 = blockIdx.x * GM_TOK, h = blockIdx.y;
+    const int D = a.dim, V = a.vdim, kvh = h / (a.n_head / a.n_head_kv);
+    const float *kb = a.k_cache + (int64_t)kvh * D, *vb = a.v_cache + (int64_t)kvh * V;
+    const bool q4 = D % 4 == 0 && a.q_stride % 4 == 0 && ((uintptr_t)a.q & 15) == 0;
+    const bool k4 = D % 4 == 0 && a.k_cache_stride % 4 == 0 && ((uintptr_t)a.k_cache & 15) == 0;
+    const bool v4 = V % 4 == 0 && a.v_cache_stride % 4 == 0 && ((uintptr_t)a.v_cache & 15) == 0;
+
+    gm_stage(qs, QSTRIDE, GM_TOK, D, KS * 16, q4, [&](int r) { return t0 + r < a.n_tokens ? a.q + (int64_t)(t0 + r) * a.q_stride + (int64_t)h * D : nullptr; });
+    // the warp's 16 tokens: lane i < 16 holds token i (for the tile test); every lane the two rows of its accumulator fragments
+    const int wt = t0 + warp * 16;
+    int my_seq = -2, my_pos = 0;
+    if (lane < 16 && wt + lane < a.n_tokens) { my_seq = a.tok_seq[wt + lane]; my_pos = a.tok_pos[wt + lane]; }
+    const int rs0 = __shfl_sync(0xffffffffu, my_seq, g), rp0 = __shfl_sync(0xffffffffu, my_pos, g);
+    const int rs1 = __shfl_sync(0xffffffffu, my_seq, g + 8), rp1 = __shfl_sync(0xffffffffu, my_pos, g + 8);
+    __syncthreads();
+
+    const int mi = lane >> 3, mr = lane & 7;
+    const unsigned qs_u = (unsigned)__cvta_generic_to_shared(qs), ks_u = (unsigned)__cvta_generic_to_shared(ks), vs_u = (unsigned)__cvta_generic_to_shared(vs);
+    const unsigned a_off = (unsigned)(((mi & 1) * 8 + mr) * QSTRIDE + (mi >> 1) * 16);   // A (queries): rows (mi&1)*8.., columns (mi>>1)*8..
+    const unsigned k_off = (unsigned)(((mi >> 1) * 8 + mr) * QSTRIDE + (mi & 1) * 16);   // B (keys): cells (mi>>1)*8.., values (mi&1)*8..
+    const unsigned v_off = (unsigned)(((mi & 1) * 8 + mr) * VSTRIDE + (mi >> 1) * 16);   // transposed B (values): cells (mi&1)*8.., columns (mi>>1)*8..
+    unsigned qa[KS][4];
+#pragma unroll
+    for (int kk = 0; kk < KS; kk++) gm_ldsm4(qs_u + warp * 16 * QSTRIDE + a_off + kk * 32, qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3]);
+    float o[2 * VS][4];
+#pragma unroll
+    for (int j = 0; j < 2 * VS; j++) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;  // rows g and g + 8; l: this lane's share of the row sum
+
+    for (int c0 = 0; c0 < a.n_kv; c0 += GM_CELLS) {
+        // does any of the warp's tokens see any of the tile's cells?  lane = cell
+        int cs = -1, cp = 0;
+        if (c0 + lane < a.n_kv) { cs = a.cell_seq[c0 + lane]; cp = a.cell_pos[c0 + lane]; }
+        bool see = false;
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            const int ts = __shfl_sync(0xffffffffu, my_seq, i), tp = __shfl_sync(0xffffffffu, my_pos, i);
+            see |= cs >= 0 && sa_visible(cs, cp, ts, tp, a.window, a.keep_first);
+        }
+        const bool warp_sees = __any_sync(0xffffffffu, see);
+        if (!__syncthreads_or(warp_sees)) continue;  // (also: the previous tile has been read by every warp)
+        if (warp == 0) { cseq[lane] = cs; cpos[lane] = cp; }
+        gm_stage(ks, QSTRIDE, GM_CELLS, D, KS * 16, k4, [&](int r) { return c0 + r < a.n_kv && a.cell_seq[c0 + r] >= 0 ? kb + (int64_t)(c0 + r) * a.k_cache_stride : nullptr; });
+        gm_stage(vs, VSTRIDE, GM_CELLS, V, VS * 16, v4, [&](int r) { return c0 + r < a.n_kv && a.cell_seq[c0 + r] >= 0 ? vb + (int64_t)(c0 + r) * a.v_cache_stride : nullptr; });
+        __syncthreads();
+        if (!warp_sees) continue;
+        float s[GM_CELLS / 8][4];
+#pragma unroll
+        for (int j = 0; j < GM_CELLS / 8; j++) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+        for (int kk = 0; kk < KS; kk++) {
+#pragma unroll
+            for (int half = 0; half < GM_CELLS / 16; half++) {
+                unsigned b0, b1, b2, b3;
+                gm_ldsm4(ks_u + half * 16 * QSTRIDE + k_off + kk * 32, b0, b1, b2, b3);
+                gm_mma_bf16(s[2 * half], qa[kk], b0, b1);
+                gm_mma_bf16(s[2 * half + 1], qa[kk], b2, b3);
+            }
+        }
+        // scale, visibility, running maximum per row (a row lives in the 4 lanes of a quad)
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < GM_CELLS / 8; j++) {
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                const int c = j * 8 + 2 * t4 + e;
+                const int xs = cseq[c], xp = cpos[c];
+                s[j][e] = sa_visible(xs, xp, rs0, rp0, a.window, a.keep_first) ? s[j][e] * a.scale : -INFINITY;
+                s[j][2 + e] = sa_visible(xs, xp, rs1, rp1, a.window, a.keep_first) ? s[j][2 + e] * a.scale : -INFINITY;
+                mx0 = fmaxf(mx0, s[j][e]); mx1 = fmaxf(mx1, s[j][2 + e]);
+            }
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+        const float al0 = n0 == -INFINITY ? 1.f : expf(m0 - n0), al1 = n1 == -INFINITY ? 1.f : expf(m1 - n1);  // nothing seen yet: keep the zeros
+        m0 = n0; m1 = n1;
+        float ps0 = 0.f, ps1 = 0.f;
+        unsigned pa[GM_CELLS / 16][4];
+#pragma unroll
+        for (int j = 0; j < GM_CELLS / 8; j++) {
+            const float p0 = n0 == -INFINITY ? 0.f : expf(s[j][0] - n0), p1 = n0 == -INFINITY ? 0.f : expf(s[j][1] - n0);
+            const float p2 = n1 == -INFINITY ? 0.f : expf(s[j][2] - n1), p3 = n1 == -INFINITY ? 0.f : expf(s[j][3] - n1);
+            ps0 += p0 + p1; ps1 += p2 + p3;
+            pa[j >> 1][(j & 1) * 2] = gm_pack_bf2(p0, p1);
+            pa[j >> 1][(j & 1) * 2 + 1] = gm_pack_bf2(p2, p3);
+        }
+        l0 = l0 * al0 + ps0; l1 = l1 * al1 + ps1;
+        const bool rescale = __any_sync(0xffffffffu, al0 != 1.f || al1 != 1.f);
+        if (rescale) {
+#pragma unroll
+            for (int j = 0; j < 2 * VS; j++) { o[j][0] *= al0; o[j][1] *= al0; o[j][2] *= al1; o[j][3] *= al1; }
+        }
+#pragma unroll
+        for (int kk = 0; kk < GM_CELLS / 16; kk++) {
+#pragma unroll
+            for (int j = 0; j < VS; j++) {
+                unsigned b0, b1, b2, b3;
+                gm_ldsm4_t(vs_u + kk * 16 * VSTRIDE + v_off + j * 32, b0, b1, b2, b3);
+                gm_mma_bf16(o[2 * j], pa[kk], b0, b1);      // columns 16 j .. 16 j + 7
+                gm_mma_bf16(o[2 * j + 1], pa[kk], b2, b3);  // columns 16 j + 8 .. 16 j + 15
+            }
+        }
+    }
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    const float sink = a.sink ? a.sink[h] : -INFINITY;
+    float w[2];
+    {
+        const float M0 = fmaxf(m0, sink), M1 = fmaxf(m1, sink);
+        const float f0 = m0 == -INFINITY ? 0.f : expf(m0 - M0), f1 = m1 == -INFINITY ? 0.f : expf(m1 - M1);
+        const float d0 = l0 * f0 + (a.sink ? expf(sink - M0) : 0.f), d1 = l1 * f1 + (a.sink ? expf(sink - M1) : 0.f);
+        w[0] = d0 > 0.f ? f0 / d0 : 0.f; w[1] = d1 > 0.f ? f1 / d1 : 0.f;
+    }
+#pragma unroll
+    for (int hh = 0; hh < 2; hh++) {
+        const int t = wt + g + 8 * hh;
+        if (t >= a.n_tokens) continue;
+        float *out = a.dst + (int64_t)t * a.dst_stride + (int64_t)h * V;
+#pragma unroll
+        for (int j = 0; j < 2 * VS; j++) {
+            const int c = 8 * j + 2 * t4;
+            if (c < V) out[c] = o[j][2 * hh] * w[hh];
+            if (c + 1 < V) out[c + 1] = o[j][2 * hh + 1] * w[hh];
+        }
+    }
+}
+
+template <int KS, int VS>
+static int launch_sink_attn_mma2(const b200_sink_attn_args *a, cudaStream_t st) {
+    const dim3 grid((unsigned)((a->n_tokens + GM_TOK - 1) / GM_TOK), (unsigned)a->n_head);
+    sink_attn_mma_kernel<KS, VS><<<grid, GM_WARPS * 32, 0, st>>>(*a);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
+template <int KS>
+static int launch_sink_attn_mma1(const b200_sink_attn_args *a, cudaStream_t st) {
+    const int vs = (a->vdim + 15) / 16;
+    if (vs <= 2) return launch_sink_attn_mma2<KS, 2>(a, st);
+    if (vs <= 4) return launch_sink_attn_mma2<KS, 4>(a, st);
+    if (vs <= 6) return launch_sink_attn_mma2<KS, 6>(a, st);
+    return launch_sink_attn_mma2<KS, 8>(a, st);
+}
+// bf16 products were asked for, there are enough tokens to fill 16-row tiles, and the head sizes fit the register budget
+static bool sink_attn_mma_ok(const b200_sink_attn_args *a) { return a->bf16_products && a->n_tokens >= 16 && a->dim <= 128 && a->vdim <= 128; }
+static int launch_sink_attn_mma(const b200_sink_attn_args *a, cudaStream_t st) {
+    const int ks = (a->dim + 15) / 16;
+    if (ks <= 2) return launch_sink_attn_mma1<2>(a, st);
+    if (ks <= 4) return launch_sink_attn_mma1<4>(a, st);
+    if (ks <= 6) return launch_sink_attn_mma1<6>(a, st);
+    return launch_sink_attn_mma1<8>(a, st);
+}
+
 // ------------------------------------------------------------------------------------------------ linear attention with decay
 // The columns of the state never interact: a warp owns LA_CW columns of one (sequence, head) and keeps them in registers over
 // the whole token loop, a lane the rows d = lane, lane + 32, ...  The inputs of LA_CHUNK tokens are staged in shared memory
@@ -275,6 +482,7 @@ extern "C" int b200_op_sink_attn(const b200_sink_attn_args *a, b200_stream_t str
                 a->n_tokens >= 0 && a->n_kv >= 0 && a->window >= 0 && a->keep_first >= 0, B200_ERR_UNSUPPORTED, "b200_op_sink_attn: head sizes up to 256, heads up to 65535");
     if (a->n_tokens == 0) return B200_OK;
     const cudaStream_t st = (cudaStream_t)stream;
+    if (sink_attn_mma_ok(a)) return launch_sink_attn_mma(a, st);
     const int nd = (a->dim + 31) / 32;
     if (nd <= 1) return launch_sink_attn<1>(a, st);
     if (nd <= 2) return launch_sink_attn<2>(a, st);
