@@ -659,9 +659,137 @@ def genesun_step_cost(cfg: dict, n_tokens: int, n_seq: int, ctx: int) -> dict:
     return {"weight_bytes": 2 * wparams, "cache_bytes": cache, "state_bytes": state, "flop": 2 * wparams * n_tokens + attn_flop}
 
 
+
+# ------------------------------------------------------------------------------------------------ --design galirax
+# The same measurement for the Galirax design (grouped-query attention with sinks / windows, lightning attention, routed gated
+# experts), beside the llama decoder with mixtral-style experts at equal width, depth, heads and expert sizes (Q4_K_M).
+GALIRAX_SIZES = {
+    # width, (heads, kv_heads, dim, vdim), (experts, per token, ff, groups, kept groups), window
+    "w1024": (1024, (8, 2, 128, 128), (8, 2, 1024, 4, 2), 512),
+    "w2048": (2048, (16, 4, 128, 128), (8, 2, 2048, 4, 2), 512),
+    "w4096": (4096, (32, 8, 128, 128), (8, 2, 2048, 4, 2), 512),
+}
+
+
+def galirax_config(size: str) -> dict:
+    import math
+    W, (h, g, d, v), (ne, top, ff, ng, nk), window = GALIRAX_SIZES[size]
+    mlp = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": ne, "top": top, "groups": {"count": ng, "keep": nk}, "scale": 2.0}}
+    rot = {"base": 500000.0, "dims": d, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
+    layers = []
+    for il in range(DESIGN_LAYERS):
+        k = il % 4
+        if k == 2:
+            layers.append({"type": "lightning", "mixer": {"heads": h, "dim": d, "vdim": v, "decay": [1.0 - 2.0 ** (-5 - 3 * i / h) for i in range(h)]}, "mlp": mlp})
+        elif k == 0:
+            layers.append({"type": "attention", "mixer": {"heads": h, "kv_heads": g, "dim": d, "vdim": v, "rot": rot, "scale": 1.0 / math.sqrt(d)}, "mlp": mlp})
+        else:
+            layers.append({"type": "attention_2", "mixer": {"heads": h, "kv_heads": g, "dim": d, "vdim": v, "rot": {"base": 10000.0, "dims": d // 2}, "scale": 1.0 / math.sqrt(d),
+                                                            "mask": {"size": window, "keep_first": 4}}, "mlp": mlp})
+    return {"architecture": "Galirax", "width": W, "vocab": DESIGN_VOCAB, "norm": {"eps": 1e-5}, "logit_softcap": 30.0, "layers": layers}
+
+
+def galirax_tensor_shapes(cfg: dict) -> dict:
+    W, V = cfg["width"], cfg["vocab"]
+    t = {"embed": (V, W), "head": (V, W), "final.norm": (W,), "final.norm.b": (W,)}
+    for i, L in enumerate(cfg["layers"]):
+        p, mx = f"l{i}.", L["mixer"]
+        H, D, Vd = mx["heads"], mx["dim"], mx["vdim"]
+        t.update({p + "norm1": (W,), p + "norm1.b": (W,), p + "mix.o": (W, H * Vd)})
+        if L["type"] == "lightning":
+            t.update({p + "mix.q": (H * D, W), p + "mix.k": (H * D, W), p + "mix.v": (H * Vd, W), p + "mix.g": (H * Vd, W), p + "mix.norm": (H * Vd,)})
+        else:
+            G = mx["kv_heads"]
+            t.update({p + "mix.q": (H * D, W), p + "mix.k": (G * D, W), p + "mix.v": (G * Vd, W), p + "mix.sink": (H,)})
+            if L["type"] == "attention_2":
+                t.update({p + "mix.q.b": (H * D,), p + "mix.k.b": (G * D,), p + "mix.v.b": (G * Vd,), p + "mix.q.norm": (H * D,), p + "mix.k.norm": (G * D,)})
+        if L["mlp"]:
+            E, F = L["mlp"]["router"]["experts"], L["mlp"]["expert"]["ff"]
+            t.update({p + "mlp.router": (E, W), p + "mlp.correction": (E,)})
+            for e in range(E):
+                t.update({f"{p}mlp.e{e}.gate": (F, W), f"{p}mlp.e{e}.up": (F, W), f"{p}mlp.e{e}.down": (W, F)})
+    return t
+
+
+def galirax_step_cost(cfg: dict, n_tokens: int, n_seq: int, ctx: int) -> dict:
+    """Algorithmic bytes (bf16 weights once -- of the experts those a batch of this size can reach --, the visible f32 cache rows and
+    the recurrent state of the batch) and FLOPs of one step."""
+    W, V = cfg["width"], cfg["vocab"]
+    wparams = W * V  # head
+    active = W * V   # parameters a token multiplies with
+    cache = state = attn_flop = 0
+    for L in cfg["layers"]:
+        mx = L["mixer"]
+        H, D, Vd = mx["heads"], mx["dim"], mx["vdim"]
+        if L["type"] == "lightning":
+            p = W * (2 * H * D + 2 * H * Vd) + W * H * Vd
+            state += n_seq * H * D * Vd * 4 * 2
+            attn_flop += 4 * n_tokens * H * D * Vd
+        else:
+            G = mx["kv_heads"]
+            p = W * (H * D + G * D + G * Vd) + W * H * Vd
+            win = (mx.get("mask") or {}).get("size", 0)
+            vis = min(ctx, win) if win else ctx
+            cache += n_seq * vis * G * (D + Vd) * 4
+            attn_flop += 2 * n_tokens * H * (vis if n_tokens == n_seq or win else ctx // 2) * (D + Vd)
+        wparams += p
+        active += p
+        if L["mlp"]:
+            r, F = L["mlp"]["router"], L["mlp"]["expert"]["ff"]
+            wparams += W * r["experts"] + 3 * W * F * min(r["experts"], n_tokens * r["top"])
+            active += W * r["experts"] + 3 * W * F * r["top"]
+    return {"weight_bytes": 2 * wparams, "cache_bytes": cache, "state_bytes": state, "flop": 2 * active * n_tokens + attn_flop}
+
+
+def galirax_llama_shape(size: str):
+    import koboldcpp_b200.llama as LL
+    W, (h, g, d, v), (ne, top, ff, ng, nk), window = GALIRAX_SIZES[size]
+    return LL.ModelShape(f"llama-moe-{size}", W, DESIGN_LAYERS, h, g, ff, DESIGN_VOCAB, "Q4_K_M", ne, top)
+
+
+def genesun_llama_shape(size: str):
+    import koboldcpp_b200.llama as LL
+    W, _, _, ff = DESIGN_SIZES[size]
+    return LL.ModelShape(f"llama-{size}", W, DESIGN_LAYERS, W // 128, W // 128, (ff + 255) // 256 * 256, DESIGN_VOCAB, "Q4_K_M")
+
+
+def random_tensors(shapes: dict, seed: int = 1):
+    """Random weights of the right shapes (one pool of N(0, 0.02) values cut into the matrices; vectors near their neutral value)."""
+    rng = np.random.default_rng(seed)
+    pool = (rng.standard_normal(1 << 24, dtype=np.float32) * 0.02)
+    pool_bits = ((pool.view(np.uint32) + 0x8000) >> 16).astype(np.uint16)
+    out, at = {}, 0
+    for name, shape in shapes.items():
+        n = int(np.prod(shape))
+        if len(shape) == 2 and name != "embed":
+            reps = -(-n // len(pool_bits))
+            bits = np.roll(pool_bits, at)[:n] if reps == 1 else np.tile(pool_bits, reps)[:n]
+            at = (at + 7919 * 13) % len(pool_bits)
+            out[name] = ("BF16", shape, bits.view(np.uint8))
+        elif name == "embed":
+            out[name] = ("F32", shape, np.resize(pool * 50, n).view(np.uint8))
+        else:
+            leaf = name.split(".")[-1]
+            v = np.full(n, 1.0, np.float32) if leaf.startswith("norm") else np.zeros(n, np.float32)
+            if leaf == "correction":
+                v[:] = np.resize(pool[:4096] * 5, n)
+            out[name] = ("F32", shape, v.view(np.uint8))
+    return out
+
+
+def design_table():
+    from koboldcpp_b200 import galirax, genesun
+    return {
+        "genesun": {"sizes": DESIGN_SIZES, "config": genesun_config, "tensors": lambda cfg: genesun_random_tensors(cfg), "cost": genesun_step_cost, "build": genesun.build,
+                    "llama": genesun_llama_shape, "beside": "llama Q4_K_M, equal width / depth / ff"},
+        "galirax": {"sizes": GALIRAX_SIZES, "config": galirax_config, "tensors": lambda cfg: random_tensors(galirax_tensor_shapes(cfg)), "cost": galirax_step_cost,
+                    "build": galirax.build, "llama": galirax_llama_shape, "beside": "llama with routed experts Q4_K_M, equal width / depth / heads / experts"},
+    }
+
 def design_leg(args) -> int:
     import koboldcpp_b200.llama as LL
-    from koboldcpp_b200 import genesun as G
+    DS = design_table()[args.design]
+    name = args.design
     from koboldcpp_b200.engine import Engine
     from koboldcpp_b200.lib import F16, check, lib
     L = lib()
@@ -695,12 +823,12 @@ def design_leg(args) -> int:
 
     steps, warmup = max(3, min(args.steps, 20)), max(3, args.warmup)
     rows = []
-    sizes = [s for s in DESIGN_SIZES if not args.design_sizes or s in args.design_sizes.split(",")]
+    sizes = [s for s in DS["sizes"] if not args.design_sizes or s in args.design_sizes.split(",")]
     for size in sizes:
-        cfg = genesun_config(size)
+        cfg = DS["config"](size)
         W = cfg["width"]
         row = {"size": size, "width": W, "layers": DESIGN_LAYERS, "ctx": DESIGN_CTX}
-        m = G.build(cfg, genesun_random_tensors(cfg), dtype="bfloat16", n_ctx=8 * DESIGN_CTX + 256, n_seq_max=8, max_batch=DESIGN_PP)
+        m = DS["build"](cfg, DS["tensors"](cfg), dtype="bfloat16", n_ctx=8 * DESIGN_CTX + 256, n_seq_max=8, max_batch=DESIGN_PP)
         eng = Engine(m)
         rng = np.random.default_rng(0)
         prompt = rng.integers(0, DESIGN_VOCAB, DESIGN_PP).tolist()
@@ -709,8 +837,8 @@ def design_leg(args) -> int:
         eng.step([("p", prompt, [DESIGN_PP - 1])])
         e2e_first = time.time() - t0
         ms = time_replay(m, m.stream, steps, warmup)
-        cost = genesun_step_cost(cfg, DESIGN_PP, 1, DESIGN_PP)
-        row["genesun_prefill"] = {"tokens": DESIGN_PP, "ms": ms, "tok_s": DESIGN_PP / ms * 1e3, "tflops": cost["flop"] / ms / 1e9,
+        cost = DS["cost"](cfg, DESIGN_PP, 1, DESIGN_PP)
+        row[f"{name}_prefill"] = {"tokens": DESIGN_PP, "ms": ms, "tok_s": DESIGN_PP / ms * 1e3, "tflops": cost["flop"] / ms / 1e9,
                                   "of_measured_bf16": cost["flop"] / ms / 1e9 / tfl, "launches": m.stats()["n_kernels"], "first_call_s": e2e_first}
         eng.finish("p")
         # decode: 1 and 8 sequences at DESIGN_CTX tokens of context each
@@ -725,23 +853,24 @@ def design_leg(args) -> int:
                 lg = eng.step([(rid, [5], [0]) for rid in ids])
             e2e_ms = (time.time() - t0) / n_e2e * 1e3
             ms = time_replay(m, m.stream, steps, warmup)
-            cost = genesun_step_cost(cfg, nseq, nseq, DESIGN_CTX)
+            cost = DS["cost"](cfg, nseq, nseq, DESIGN_CTX)
             byt = cost["weight_bytes"] + cost["cache_bytes"] + cost["state_bytes"]
-            row[f"genesun_decode_b{nseq}"] = {"ms": ms, "tok_s": nseq / ms * 1e3, "e2e_ms": e2e_ms, "e2e_tok_s": nseq / e2e_ms * 1e3, "alg_bytes": byt, "gbs": byt / ms / 1e6,
+            row[f"{name}_decode_b{nseq}"] = {"ms": ms, "tok_s": nseq / ms * 1e3, "e2e_ms": e2e_ms, "e2e_tok_s": nseq / e2e_ms * 1e3, "alg_bytes": byt, "gbs": byt / ms / 1e6,
                                               "of_measured_hbm": byt / ms / 1e6 / hbm_gbs, "launches": m.stats()["n_kernels"], "finite": bool(np.isfinite(lg).all())}
             for rid in ids:
                 eng.finish(rid)
         m.close()
         # the llama decoder at equal width, depth and feed-forward size
-        _, (h, d, r, v, kr, qr), _, ff = DESIGN_SIZES[size]
-        shape = LL.ModelShape(f"llama-{size}", W, DESIGN_LAYERS, W // 128, W // 128, (ff + 255) // 256 * 256, DESIGN_VOCAB, "Q4_K_M")
+        shape = DS["llama"](size)
         lm = LL.LlamaModel(shape, DESIGN_CTX + 256, F16)
         lm.init_random(seed=3)
         lm.finalize(max_batch=DESIGN_PP)
         lm.kv_fill_random(DESIGN_CTX, seed=7)
         lm.decode(prompt, 0)
         ms = time_replay(lm, lm.stream, steps, warmup)
-        lflop = 2 * DESIGN_PP * (shape.n_layer * (4 * W * W + 3 * W * shape.n_ff) + W * DESIGN_VOCAB) + 4 * DESIGN_PP * (DESIGN_PP // 2) * W * shape.n_layer
+        kvw = W * shape.n_head_kv // shape.n_head
+        lflop = 2 * DESIGN_PP * (shape.n_layer * (2 * W * W + 2 * W * kvw + 3 * W * shape.n_ff * max(1, shape.n_expert_used) + W * shape.n_expert) + W * DESIGN_VOCAB) + \
+            4 * DESIGN_PP * (DESIGN_PP // 2) * W * shape.n_layer
         row["llama_prefill"] = {"tokens": DESIGN_PP, "ms": ms, "tok_s": DESIGN_PP / ms * 1e3, "tflops": lflop / ms / 1e9, "of_measured_bf16": lflop / ms / 1e9 / tfl,
                                 "launches": lm.stats()["n_kernels"]}
         lm.kv_fill_random(DESIGN_CTX, seed=7)
@@ -752,7 +881,7 @@ def design_leg(args) -> int:
         lm.close()
         rows.append(row)
         print(json.dumps({"design_size": row}), file=sys.stderr, flush=True)
-    print(json.dumps({"design": "genesun", "beside": "llama Q4_K_M, equal width / depth / ff", "dtype": "bf16", "data": "synthetic", "steps": steps, "warmup": warmup,
+    print(json.dumps({"design": name, "beside": DS["beside"], "dtype": "bf16", "data": "synthetic", "steps": steps, "warmup": warmup,
                       "timing": "CUDA events around the replayed step graph, 256 MB L2 flush before each", "sizes": rows}))
     return 0
 
@@ -768,7 +897,7 @@ def main() -> int:
     ap.add_argument("--cpu-budget", type=float, default=18.0)
     ap.add_argument("--no-tp70", action="store_true", default=bool(os.environ.get("B200_BENCH_NO_TP70")),
                     help="skip the auxiliary 70B tensor-parallel leg (BASELINE.json configs[4])")
-    ap.add_argument("--design", default="", choices=["", "genesun"],
+    ap.add_argument("--design", default="", choices=["", "genesun", "galirax"],
                     help="instead of the default workload: prefill / decode of this design at real layer shapes beside the llama decoder at equal size")
     ap.add_argument("--design-sizes", default="", help="comma-separated subset of " + ",".join(DESIGN_SIZES))
     args = ap.parse_args()

@@ -246,6 +246,10 @@ typedef struct {
     int32_t bf16_products;
 } b200_sink_attn_args;
 B200_API int b200_op_sink_attn(const b200_sink_attn_args *a, b200_stream_t stream);
+/* The same with a workspace of b200_sink_attn_workspace_bytes(a) bytes (16-byte aligned; 0: none needed): with few tokens and
+ * many cells (decode) the cells of a (token, head) pair are split over several CTAs whose partial results meet there. */
+B200_API size_t b200_sink_attn_workspace_bytes(const b200_sink_attn_args *a);
+B200_API int b200_op_sink_attn_ws(const b200_sink_attn_args *a, void *workspace, size_t workspace_bytes, b200_stream_t stream);
 
 /* Linear attention with a decayed state per (slot, head), f32: S' = decay[h] S + k v^T, o = S'^T q, over the tokens of n_seq
  * sequences; act != 0 applies silu to q, k and v first.  seq_info as for b200_op_mlstm_scan.  State [head][vdim][dim] per slot.

@@ -94,6 +94,19 @@ static bool ext_op_supported(const ggml_tensor *op) {
     }
 }
 
+static void fill_sink_attn_args(const ggml_tensor *n, b200_sink_attn_args &a) {
+    const ggml_tensor *const *s = n->src;
+    memset(&a, 0, sizeof(a));
+    a.dim = n->op_params[2]; a.vdim = n->op_params[7]; a.scale = ext_f(n, 3); a.window = n->op_params[4]; a.keep_first = n->op_params[5]; a.bf16_products = n->op_params[6];
+    a.q = (const float *)s[0]->data; a.q_stride = (int64_t)(s[0]->nb[1] / 4); a.n_head = (int32_t)(s[0]->ne[0] / a.dim); a.n_tokens = (int32_t)s[0]->ne[1];
+    a.k_cache = (const float *)s[1]->data; a.k_cache_stride = (int64_t)(s[1]->nb[1] / 4); a.n_head_kv = (int32_t)(s[1]->ne[0] / a.dim);
+    a.v_cache = (const float *)s[2]->data; a.v_cache_stride = (int64_t)(s[2]->nb[1] / 4);
+    a.sink = s[3] ? (const float *)s[3]->data : nullptr;
+    a.tok_seq = (const int32_t *)s[4]->data; a.tok_pos = (const int32_t *)s[5]->data;
+    a.cell_seq = (const int32_t *)s[6]->data; a.cell_pos = (const int32_t *)s[7]->data; a.n_kv = (int32_t)s[6]->ne[0];
+    a.dst = (float *)n->data; a.dst_stride = (int64_t)(n->nb[1] / 4);
+}
+
 // the batched tensor-core form of an expert product over bf16 weights (the grouped GEMM of the quantised types)
 static bool ext_mul_mat_id_gemm_ok(const ggml_tensor *n) {
     const ggml_tensor *as = n->src[0], *b = n->src[1], *ids = n->src[2];
@@ -193,16 +206,11 @@ static void run_ext(ExecCtx &x, const ggml_tensor *n) {
         }
         case B200_EXT_SINK_ATTN: {
             b200_sink_attn_args a;
-            memset(&a, 0, sizeof(a));
-            a.dim = n->op_params[2]; a.vdim = n->op_params[7]; a.scale = ext_f(n, 3); a.window = n->op_params[4]; a.keep_first = n->op_params[5]; a.bf16_products = n->op_params[6];
-            a.q = (const float *)s[0]->data; a.q_stride = (int64_t)(s[0]->nb[1] / 4); a.n_head = (int32_t)(s[0]->ne[0] / a.dim); a.n_tokens = (int32_t)s[0]->ne[1];
-            a.k_cache = (const float *)s[1]->data; a.k_cache_stride = (int64_t)(s[1]->nb[1] / 4); a.n_head_kv = (int32_t)(s[1]->ne[0] / a.dim);
-            a.v_cache = (const float *)s[2]->data; a.v_cache_stride = (int64_t)(s[2]->nb[1] / 4);
-            a.sink = s[3] ? (const float *)s[3]->data : nullptr;
-            a.tok_seq = (const int32_t *)s[4]->data; a.tok_pos = (const int32_t *)s[5]->data;
-            a.cell_seq = (const int32_t *)s[6]->data; a.cell_pos = (const int32_t *)s[7]->data; a.n_kv = (int32_t)s[6]->ne[0];
-            a.dst = (float *)n->data; a.dst_stride = (int64_t)(n->nb[1] / 4);
-            B200_CHECK_RC(b200_op_sink_attn(&a, x.stream));
+            fill_sink_attn_args(n, a);
+            const size_t need = b200_sink_attn_workspace_bytes(&a);
+            if (need > 0) x.xb_src = nullptr;  // the scratch no longer holds a product's converted activations
+            B200_CHECK_RC(b200_op_sink_attn_ws(&a, need <= x.scratch_bytes ? x.scratch : nullptr, x.scratch_bytes, x.stream));
+            x.launches += need > 0 && need <= x.scratch_bytes ? 1 : 0;
             break;
         }
         case B200_EXT_LINEAR_ATTN_SCAN: {
@@ -584,6 +592,11 @@ size_t node_scratch_bytes(const ggml_tensor *n) {
         const ggml_tensor *w = n->src[0], *a = n->src[1];
         const size_t one = b200_mul_mat_q_workspace_bytes(w->type, w->ne[0], w->ne[1], a->ne[1]);
         return (a->ne[2] > 1 && a->ne[3] == 1 && w->ne[2] == a->ne[2]) ? one * (size_t)a->ne[2] : one;
+    }
+    if (n->op == GGML_OP_MAP_CUSTOM1 && (uint32_t)n->op_params[0] == B200_EXT_TAG && n->op_params[1] == B200_EXT_SINK_ATTN) {
+        b200_sink_attn_args a;
+        fill_sink_attn_args(n, a);
+        return b200_sink_attn_workspace_bytes(&a);
     }
     if (n->op == GGML_OP_MAP_CUSTOM1 && (uint32_t)n->op_params[0] == B200_EXT_TAG && n->op_params[1] == B200_EXT_MUL_MAT_ID && ext_mul_mat_id_gemm_ok(n))
         return b200_mul_mat_id_q_workspace_bytes(n->src[0]->type, n->src[0]->ne[0], n->src[0]->ne[1], n->src[2]->ne[0], n->src[2]->ne[1], (int32_t)n->src[0]->ne[2]);

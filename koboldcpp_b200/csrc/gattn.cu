@@ -13,7 +13,7 @@ using namespace opx;
 // ------------------------------------------------------------------------------------------------ bias + norm + rotation + cache store
 // One CTA per token.  The RMS statistics run over the whole projection (all heads at once); q is rewritten in place, k and v go
 // to the token's cache rows.
-__global__ void __launch_bounds__(256) qkv_store_kernel(const b200_qkv_store_args a) {
+__global__ void __launch_bounds__(1024) qkv_store_kernel(const b200_qkv_store_args a) {
     __shared__ float sh[32];
     const int t = blockIdx.x;
     const int nq = a.n_head * a.dim, nk = a.n_head_kv * a.dim, nv = a.n_head_kv * a.vdim;
@@ -71,8 +71,10 @@ __device__ __forceinline__ bool sa_visible(int cell_seq, int cell_pos, int seq, 
 // online softmax and an accumulator; they meet in shared memory, where the sink joins the denominator.
 // ND = ceil(dim / 32), NV = ceil(vdim / 32): values per lane.  WARPS is 16 when there are few (token, head) pairs (decode).
 constexpr int SA_UNROLL = 4;
+// With n_split > 1 (few tokens, many cells) blockIdx.z takes one stretch of the cells and leaves (maximum, sum, unnormalised
+// accumulator) in `part`; sink_attn_merge_kernel joins the stretches and the sink.
 template <int ND, int NV, int WARPS>
-__global__ void __launch_bounds__(WARPS * 32) sink_attn_kernel(const b200_sink_attn_args a) {
+__global__ void __launch_bounds__(WARPS * 32) sink_attn_kernel(const b200_sink_attn_args a, float *__restrict__ part, int n_split) {
     extern __shared__ float smem[];  // [WARPS][vdim] accumulators, then m[WARPS], l[WARPS]
     const int t = blockIdx.x, h = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -87,9 +89,11 @@ __global__ void __launch_bounds__(WARPS * 32) sink_attn_kernel(const b200_sink_a
     for (int i = 0; i < NV; i++) acc[i] = 0.f;
     const int seq = a.tok_seq[t], pos = a.tok_pos[t];
     float m = -INFINITY, l = 0.f;
-    for (int cb = warp * 32; cb < a.n_kv; cb += WARPS * 32) {
+    const int per_split = ((a.n_kv + n_split - 1) / n_split + 31) & ~31;
+    const int c_begin = (int)blockIdx.z * per_split, c_end = min(a.n_kv, c_begin + per_split);
+    for (int cb = c_begin + warp * 32; cb < c_end; cb += WARPS * 32) {
         bool mine = false;
-        if (cb + lane < a.n_kv) mine = sa_visible(a.cell_seq[cb + lane], a.cell_pos[cb + lane], seq, pos, a.window, a.keep_first);
+        if (cb + lane < c_end) mine = sa_visible(a.cell_seq[cb + lane], a.cell_pos[cb + lane], seq, pos, a.window, a.keep_first);
         unsigned rest = __ballot_sync(0xffffffffu, mine);
         while (rest) {
             bool vis[SA_UNROLL];  // warp-uniform
@@ -137,14 +141,24 @@ __global__ void __launch_bounds__(WARPS * 32) sink_attn_kernel(const b200_sink_a
     for (int i = 0; i < NV; i++) { const int j = lane + 32 * i; if (j < V) sacc[j] = acc[i]; }
     if (lane == 0) { sm[warp] = m; sl[warp] = l; }
     __syncthreads();
-    const float sink = a.sink ? a.sink[h] : -INFINITY;
+    const float sink = (a.sink && n_split == 1) ? a.sink[h] : -INFINITY;  // split: the merge adds the sink
     float M = sink;
     for (int w = 0; w < WARPS; w++) M = fmaxf(M, sm[w]);
-    float L = a.sink ? expf(sink - M) : 0.f;
+    float L = sink != -INFINITY ? expf(sink - M) : 0.f;
     for (int w = 0; w < WARPS; w++) if (sm[w] != -INFINITY) L += sl[w] * expf(sm[w] - M);
     __syncthreads();
     if (threadIdx.x < WARPS) sl[threadIdx.x] = sm[threadIdx.x] == -INFINITY ? 0.f : expf(sm[threadIdx.x] - M);  // the warp's weight in the merge
     __syncthreads();
+    if (n_split > 1) {
+        float *pp = part + (((int64_t)t * a.n_head + h) * n_split + blockIdx.z) * (V + 2);
+        if (threadIdx.x == 0) { pp[0] = M; pp[1] = L; }
+        for (int j = threadIdx.x; j < V; j += blockDim.x) {
+            float o = 0.f;
+            for (int w = 0; w < WARPS; w++) o += smem[(size_t)w * V + j] * sl[w];
+            pp[2 + j] = o;
+        }
+        return;
+    }
     const float inv = L > 0.f ? 1.0f / L : 0.f;
     float *out = a.dst + (int64_t)t * a.dst_stride + (int64_t)h * V;
     for (int j = threadIdx.x; j < V; j += blockDim.x) {
@@ -154,26 +168,62 @@ __global__ void __launch_bounds__(WARPS * 32) sink_attn_kernel(const b200_sink_a
     }
 }
 
+// one CTA per (token, head), a thread per output column: the stretches' (maximum, sum, accumulator) and the sink become the output row
+__global__ void __launch_bounds__(128) sink_attn_merge_kernel(const b200_sink_attn_args a, const float *__restrict__ part, int n_split) {
+    const int64_t pair = blockIdx.x;
+    const int V = a.vdim, h = (int)(pair % a.n_head);
+    const int64_t t = pair / a.n_head;
+    const float *pp = part + pair * n_split * (V + 2);
+    const float sink = a.sink ? a.sink[h] : -INFINITY;
+    float M = sink;
+    for (int z = 0; z < n_split; z++) M = fmaxf(M, pp[(int64_t)z * (V + 2)]);
+    float L = a.sink ? expf(sink - M) : 0.f;
+    for (int z = 0; z < n_split; z++) { const float mz = pp[(int64_t)z * (V + 2)]; if (mz != -INFINITY) L += pp[(int64_t)z * (V + 2) + 1] * expf(mz - M); }
+    const float inv = L > 0.f ? 1.0f / L : 0.f;
+    float *out = a.dst + t * a.dst_stride + (int64_t)h * V;
+    for (int j = threadIdx.x; j < V; j += blockDim.x) {
+        float o = 0.f;
+        for (int z = 0; z < n_split; z++) { const float mz = pp[(int64_t)z * (V + 2)]; if (mz != -INFINITY) o += pp[(int64_t)z * (V + 2) + 2 + j] * expf(mz - M); }
+        out[j] = o * inv;
+    }
+}
+
+// stretches of cells per (token, head) when there are too few pairs to fill the device (decode) and a workspace to merge through
+static int sink_attn_splits(const b200_sink_attn_args *a) {
+    const int64_t pairs = (int64_t)a->n_tokens * a->n_head;
+    // a batch of several sequences fills the device by itself, and its stretches would be unequal; below a few thousand cells a
+    // pair's CTA is bound by its fixed costs, not by the cells, and the merge would only add a launch
+    if (pairs * 2 > 148 || a->n_kv < 2048) return 1;
+    int s = (int)((2 * 148 + pairs - 1) / pairs);
+    const int most = a->n_kv / 128;  // at least 128 cells per stretch
+    if (s > most) s = most;
+    if (s > 64) s = 64;
+    return s < 1 ? 1 : s;
+}
 template <int ND, int NV, int WARPS>
-static int launch_sink_attn3(const b200_sink_attn_args *a, cudaStream_t st) {
-    const dim3 grid((unsigned)a->n_tokens, (unsigned)a->n_head);
+static int launch_sink_attn3(const b200_sink_attn_args *a, float *part, int n_split, cudaStream_t st) {
+    const dim3 grid((unsigned)a->n_tokens, (unsigned)a->n_head, (unsigned)n_split);
     const size_t smem = ((size_t)WARPS * a->vdim + 2 * WARPS) * 4;
-    sink_attn_kernel<ND, NV, WARPS><<<grid, WARPS * 32, smem, st>>>(*a);
+    sink_attn_kernel<ND, NV, WARPS><<<grid, WARPS * 32, smem, st>>>(*a, part, n_split);
     B200_CUDA_TRY(cudaGetLastError());
+    if (n_split > 1) {
+        sink_attn_merge_kernel<<<(unsigned)(a->n_tokens * a->n_head), 128, 0, st>>>(*a, part, n_split);
+        B200_CUDA_TRY(cudaGetLastError());
+    }
     return B200_OK;
 }
 template <int ND, int NV>
-static int launch_sink_attn2(const b200_sink_attn_args *a, cudaStream_t st) {
-    if ((int64_t)a->n_tokens * a->n_head < 2 * 148 && a->n_kv > 64) return launch_sink_attn3<ND, NV, 16>(a, st);
-    return launch_sink_attn3<ND, NV, 4>(a, st);
+static int launch_sink_attn2(const b200_sink_attn_args *a, float *part, int n_split, cudaStream_t st) {
+    if ((int64_t)a->n_tokens * a->n_head < 2 * 148 && a->n_kv > 64) return launch_sink_attn3<ND, NV, 16>(a, part, n_split, st);
+    return launch_sink_attn3<ND, NV, 4>(a, part, 1, st);
 }
 template <int ND>
-static int launch_sink_attn(const b200_sink_attn_args *a, cudaStream_t st) {
+static int launch_sink_attn(const b200_sink_attn_args *a, float *part, int n_split, cudaStream_t st) {
     const int nv = (a->vdim + 31) / 32;
-    if (nv <= 1) return launch_sink_attn2<ND, 1>(a, st);
-    if (nv <= 2) return launch_sink_attn2<ND, 2>(a, st);
-    if (nv <= 4) return launch_sink_attn2<ND, 4>(a, st);
-    return launch_sink_attn2<ND, 8>(a, st);
+    if (nv <= 1) return launch_sink_attn2<ND, 1>(a, part, n_split, st);
+    if (nv <= 2) return launch_sink_attn2<ND, 2>(a, part, n_split, st);
+    if (nv <= 4) return launch_sink_attn2<ND, 4>(a, part, n_split, st);
+    return launch_sink_attn2<ND, 8>(a, part, n_split, st);
 }
 
 // ------------------------------------------------------------------------------------------------ attention, bf16 products (prompts)
@@ -387,18 +437,19 @@ static int launch_sink_attn_mma(const b200_sink_attn_args *a, cudaStream_t st) {
 // The columns of the state never interact: a warp owns LA_CW columns of one (sequence, head) and keeps them in registers over
 // the whole token loop, a lane the rows d = lane, lane + 32, ...  The inputs of LA_CHUNK tokens are staged in shared memory
 // (activation applied once) while the serial loop only does the decayed rank-one update and the column sums.
-constexpr int LA_CW = 4, LA_WARPS = 4, LA_COLS = LA_CW * LA_WARPS, LA_CHUNK = 16;
+constexpr int LA_CW = 4, LA_WARPS = 4, LA_COLS = LA_CW * LA_WARPS, LA_CHUNK = 16, LA_RG = 8;
+static_assert(LA_RG * LA_CW == 32 && LA_CW == 4, "one partial sum per lane");
 __device__ __forceinline__ float la_act(float x, int act) { return act ? x / (1.0f + expf(-x)) : x; }
 template <int DPL>
 __global__ void __launch_bounds__(LA_WARPS * 32) linear_attn_scan_kernel(const b200_linear_attn_args a) {
-    extern __shared__ float sm_[];  // q [LA_CHUNK][dim], k [LA_CHUNK][dim], v [LA_CHUNK][LA_COLS]
+    extern __shared__ float sm_[];  // q [LA_CHUNK][32 DPL], k [LA_CHUNK][32 DPL], v [LA_CHUNK][LA_COLS]
     const int h = blockIdx.y, s = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
     const int D = a.dim, V = a.vdim;
     const int first = a.seq_info[s], count = a.seq_info[a.n_seq + s], slot = a.seq_info[2 * a.n_seq + s], fresh = a.seq_info[3 * a.n_seq + s];
     if (count <= 0) return;
     const int cb = blockIdx.x * LA_COLS, col0 = cb + warp * LA_CW;
-    float *sq = sm_, *sk = sq + LA_CHUNK * D, *sv = sk + LA_CHUNK * D;
+    float *sq = sm_, *sk = sq + LA_CHUNK * 32 * DPL, *sv = sk + LA_CHUNK * 32 * DPL;  // rows padded to 32 DPL values
     float *Sp = a.state + (int64_t)slot * a.slot_stride + ((int64_t)h * V + col0) * D;
     const float decay = a.decay[h];
     float S[LA_CW][DPL];
@@ -408,40 +459,71 @@ __global__ void __launch_bounds__(LA_WARPS * 32) linear_attn_scan_kernel(const b
 #pragma unroll
         for (int c = 0; c < LA_CW; c++) S[c][i] = (!fresh && d < D && col0 + c < V) ? Sp[(int64_t)c * D + d] : 0.f;
     }
+    // the inputs of the next chunk travel to registers while the current chunk is worked on: a chunk costs one trip to L2 / HBM that
+    // overlaps the serial loop instead of standing in front of it
+    constexpr int DP = 32 * DPL, NQ = LA_CHUNK * DP / (LA_WARPS * 32), NVV = LA_CHUNK * LA_COLS / (LA_WARPS * 32);
+    float pq[NQ], pk[NQ], pv[NVV];
+    auto fetch = [&](int t0) {
+        const int nt = min(LA_CHUNK, count - t0);
+#pragma unroll
+        for (int j = 0; j < NQ; j++) {
+            const int idx = tid + j * LA_WARPS * 32, tt = idx / DP, d = idx - tt * DP;
+            const bool ok = tt < nt && d < D;
+            const int64_t tok = first + t0 + tt;
+            pq[j] = ok ? a.q[tok * a.q_stride + (int64_t)h * D + d] : 0.f;
+            pk[j] = ok ? a.k[tok * a.k_stride + (int64_t)h * D + d] : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < NVV; j++) {
+            const int idx = tid + j * LA_WARPS * 32, tt = idx / LA_COLS, c = idx - tt * LA_COLS;
+            pv[j] = (tt < nt && cb + c < V) ? a.v[(int64_t)(first + t0 + tt) * a.v_stride + (int64_t)h * V + cb + c] : 0.f;
+        }
+    };
+    fetch(0);
     for (int t0 = 0; t0 < count; t0 += LA_CHUNK) {
         const int nt = min(LA_CHUNK, count - t0);
         __syncthreads();  // the previous chunk has been read
-        for (int idx = tid; idx < nt * D; idx += LA_WARPS * 32) {
-            const int tt = idx / D, d = idx - tt * D;
-            const int64_t tok = first + t0 + tt;
-            sq[idx] = la_act(a.q[tok * a.q_stride + (int64_t)h * D + d], a.act);
-            sk[idx] = la_act(a.k[tok * a.k_stride + (int64_t)h * D + d], a.act);
-        }
-        for (int idx = tid; idx < nt * LA_COLS; idx += LA_WARPS * 32) {
-            const int tt = idx / LA_COLS, c = idx - tt * LA_COLS;
-            const int64_t tok = first + t0 + tt;
-            sv[idx] = cb + c < V ? la_act(a.v[tok * a.v_stride + (int64_t)h * V + cb + c], a.act) : 0.f;
-        }
+#pragma unroll
+        for (int j = 0; j < NQ; j++) { sq[tid + j * LA_WARPS * 32] = la_act(pq[j], a.act); sk[tid + j * LA_WARPS * 32] = la_act(pk[j], a.act); }
+#pragma unroll
+        for (int j = 0; j < NVV; j++) sv[tid + j * LA_WARPS * 32] = la_act(pv[j], a.act);
         __syncthreads();
-        for (int tt = 0; tt < nt; tt++) {
-            float qv[DPL], kv[DPL], part[LA_CW];
+        if (t0 + LA_CHUNK < count) fetch(t0 + LA_CHUNK);
+        for (int tt0 = 0; tt0 < nt; tt0 += LA_RG) {
+            // the row sums do not feed the recurrence: LA_RG tokens x LA_CW columns = 32 partial sums per lane are added up across
+            // the warp in one halving exchange (31 shuffles) that leaves sum p in lane p, instead of a full reduction per sum
+            float part[LA_RG * LA_CW];
 #pragma unroll
-            for (int i = 0; i < DPL; i++) { const int d = lane + 32 * i; qv[i] = d < D ? sq[tt * D + d] : 0.f; kv[i] = d < D ? sk[tt * D + d] : 0.f; }
+            for (int u = 0; u < LA_RG; u++) {
+                const int tt = tt0 + u;
+                if (tt < nt) {  // warp-uniform
+                    float qv[DPL], kv[DPL];
 #pragma unroll
-            for (int c = 0; c < LA_CW; c++) {
-                const float vc = sv[tt * LA_COLS + warp * LA_CW + c];
-                part[c] = 0.f;
+                    for (int i = 0; i < DPL; i++) { const int d = lane + 32 * i; qv[i] = sq[tt * DP + d]; kv[i] = sk[tt * DP + d]; }
 #pragma unroll
-                for (int i = 0; i < DPL; i++) { S[c][i] = decay * S[c][i] + kv[i] * vc; part[c] += S[c][i] * qv[i]; }
+                    for (int c = 0; c < LA_CW; c++) {
+                        const float vc = sv[tt * LA_COLS + warp * LA_CW + c];
+                        float acc = 0.f;
+#pragma unroll
+                        for (int i = 0; i < DPL; i++) { S[c][i] = decay * S[c][i] + kv[i] * vc; acc += S[c][i] * qv[i]; }
+                        part[u * LA_CW + c] = acc;
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < LA_CW; c++) part[u * LA_CW + c] = 0.f;
+                }
             }
 #pragma unroll
-            for (int c = 0; c < LA_CW; c++) part[c] = warp_sum(part[c]);
-            if (lane < LA_CW && col0 + lane < V) {
-                float o = part[0];
+            for (int off = 16, n = 32; off >= 1; off >>= 1, n >>= 1) {
+                const bool upper = (lane & off) != 0;
 #pragma unroll
-                for (int c = 1; c < LA_CW; c++) if (lane == c) o = part[c];
-                a.dst[(int64_t)(first + t0 + tt) * a.dst_stride + (int64_t)h * V + col0 + lane] = o;
+                for (int i = 0; i < n / 2; i++) {
+                    const float send = upper ? part[i] : part[i + n / 2], keep = upper ? part[i + n / 2] : part[i];
+                    part[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+                }
             }
+            const int tt = tt0 + (lane >> 2), c = lane & 3;  // LA_CW == 4
+            if (tt < nt && col0 + c < V) a.dst[(int64_t)(first + t0 + tt) * a.dst_stride + (int64_t)h * V + col0 + c] = part[0];
         }
     }
 #pragma unroll
@@ -455,7 +537,7 @@ __global__ void __launch_bounds__(LA_WARPS * 32) linear_attn_scan_kernel(const b
 template <int DPL>
 static int launch_linear_attn(const b200_linear_attn_args *a, cudaStream_t st) {
     const dim3 grid((unsigned)((a->vdim + LA_COLS - 1) / LA_COLS), (unsigned)a->heads, (unsigned)a->n_seq);
-    const size_t smem = (size_t)LA_CHUNK * (2 * a->dim + LA_COLS) * 4;
+    const size_t smem = (size_t)LA_CHUNK * (2 * 32 * DPL + LA_COLS) * 4;
     linear_attn_scan_kernel<DPL><<<grid, LA_WARPS * 32, smem, st>>>(*a);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
@@ -471,23 +553,37 @@ extern "C" int b200_op_qkv_store(const b200_qkv_store_args *a, b200_stream_t str
                 a->n_tokens >= 0 && a->k_cache_stride >= (int64_t)a->n_head_kv * a->dim && a->v_cache_stride >= (int64_t)a->n_head_kv * a->vdim, B200_ERR_INVALID,
                 "b200_op_qkv_store: bad sizes");
     if (a->n_tokens == 0) return B200_OK;
-    qkv_store_kernel<<<(unsigned)a->n_tokens, 256, 0, (cudaStream_t)stream>>>(*a);
+    // few tokens (decode): a token's row is all the parallelism there is, so its CTA is wide
+    const int threads = a->n_tokens <= 64 ? 1024 : 256;
+    qkv_store_kernel<<<(unsigned)a->n_tokens, threads, 0, (cudaStream_t)stream>>>(*a);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
 }
 
-extern "C" int b200_op_sink_attn(const b200_sink_attn_args *a, b200_stream_t stream) {
+extern "C" size_t b200_sink_attn_workspace_bytes(const b200_sink_attn_args *a) {
+    if (!a || a->n_tokens <= 0 || a->n_head <= 0 || a->vdim <= 0) return 0;
+    if (a->bf16_products && a->n_tokens >= 16 && a->dim <= 128 && a->vdim <= 128) return 0;
+    const int s = sink_attn_splits(a);
+    return s > 1 ? (size_t)a->n_tokens * a->n_head * s * (a->vdim + 2) * sizeof(float) : 0;
+}
+
+extern "C" int b200_op_sink_attn(const b200_sink_attn_args *a, b200_stream_t stream) { return b200_op_sink_attn_ws(a, nullptr, 0, stream); }
+
+extern "C" int b200_op_sink_attn_ws(const b200_sink_attn_args *a, void *workspace, size_t workspace_bytes, b200_stream_t stream) {
     OPX_REQUIRE(a && a->q && a->k_cache && a->v_cache && a->cell_seq && a->cell_pos && a->tok_seq && a->tok_pos && a->dst, B200_ERR_INVALID, "b200_op_sink_attn: NULL argument");
     OPX_REQUIRE(a->n_head > 0 && a->n_head <= 65535 && a->n_head_kv > 0 && a->n_head % a->n_head_kv == 0 && a->dim > 0 && a->dim <= 256 && a->vdim > 0 && a->vdim <= 256 &&
                 a->n_tokens >= 0 && a->n_kv >= 0 && a->window >= 0 && a->keep_first >= 0, B200_ERR_UNSUPPORTED, "b200_op_sink_attn: head sizes up to 256, heads up to 65535");
     if (a->n_tokens == 0) return B200_OK;
     const cudaStream_t st = (cudaStream_t)stream;
     if (sink_attn_mma_ok(a)) return launch_sink_attn_mma(a, st);
+    int n_split = sink_attn_splits(a);
+    if (n_split > 1 && (!workspace || workspace_bytes < b200_sink_attn_workspace_bytes(a) || ((uintptr_t)workspace & 15))) n_split = 1;  // no room to merge through
+    float *part = (float *)workspace;
     const int nd = (a->dim + 31) / 32;
-    if (nd <= 1) return launch_sink_attn<1>(a, st);
-    if (nd <= 2) return launch_sink_attn<2>(a, st);
-    if (nd <= 4) return launch_sink_attn<4>(a, st);
-    return launch_sink_attn<8>(a, st);
+    if (nd <= 1) return launch_sink_attn<1>(a, part, n_split, st);
+    if (nd <= 2) return launch_sink_attn<2>(a, part, n_split, st);
+    if (nd <= 4) return launch_sink_attn<4>(a, part, n_split, st);
+    return launch_sink_attn<8>(a, part, n_split, st);
 }
 
 extern "C" int b200_op_linear_attn_scan(const b200_linear_attn_args *a, b200_stream_t stream) {

@@ -181,6 +181,8 @@ _OPS_SIGS = {
     "b200_op_silu_mul_strided": (C.c_int, [C.POINTER(Tensor), C.POINTER(Tensor), C.POINTER(Tensor), C.c_void_p]),
     "b200_op_qkv_store": (C.c_int, [C.POINTER(QkvStoreArgs), C.c_void_p]),
     "b200_op_sink_attn": (C.c_int, [C.POINTER(SinkAttnArgs), C.c_void_p]),
+    "b200_sink_attn_workspace_bytes": (C.c_size_t, [C.POINTER(SinkAttnArgs)]),
+    "b200_op_sink_attn_ws": (C.c_int, [C.POINTER(SinkAttnArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
     "b200_op_linear_attn_scan": (C.c_int, [C.POINTER(LinearAttnArgs), C.c_void_p]),
     "b200_op_moe_route_grouped": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                             C.c_float, C.c_int64, C.c_void_p]),

@@ -96,8 +96,14 @@ def run_sink_attn(q, kc, vc, cell_seq, cell_pos, tok_seq, tok_pos, sink, scale, 
     a = SinkAttnArgs(q=bufs[0].ptr, q_stride=Hh * D, k_cache=bufs[1].ptr, k_cache_stride=kc.shape[1], v_cache=bufs[2].ptr, v_cache_stride=vc.shape[1], cell_seq=bufs[3].ptr,
                      cell_pos=bufs[4].ptr, tok_seq=bufs[5].ptr, tok_pos=bufs[6].ptr, sink=dsink.ptr if dsink else None, dst=out.ptr, dst_stride=Hh * V, n_head=Hh, n_head_kv=G,
                      dim=D, vdim=V, n_tokens=T, n_kv=len(cell_seq), window=window, keep_first=keep_first, scale=scale, bf16_products=bf16)
-    check(lib().b200_op_sink_attn(C.byref(a), None))
-    return out.to_numpy(np.float32, (T, Hh, V))
+    need = int(lib().b200_sink_attn_workspace_bytes(C.byref(a)))  # > 0: few tokens and many cells, the cells are split over CTAs
+    ws = H.DeviceBuffer(need + 256) if need else None
+    check(lib().b200_op_sink_attn_ws(C.byref(a), ws.ptr if ws else None, need, None))
+    got = out.to_numpy(np.float32, (T, Hh, V))
+    if need:  # without a workspace the unsplit form must give the same
+        check(lib().b200_op_sink_attn(C.byref(a), None))
+        assert np.allclose(out.to_numpy(np.float32, (T, Hh, V)), got, rtol=1e-5, atol=1e-6, equal_nan=True)
+    return got
 
 
 def one_token_reference(q_t, kc, vc, cell_seq, cell_pos, s, p, sink, scale, G, window, keep_first):
@@ -111,10 +117,12 @@ def one_token_reference(q_t, kc, vc, cell_seq, cell_pos, s, p, sink, scale, G, w
 
 @pytest.mark.parametrize("Hh,G,D,V", [(4, 2, 16, 24), (3, 3, 40, 8), (8, 1, 64, 64), (2, 2, 96, 130), (1, 1, 200, 33)])
 @pytest.mark.parametrize("window,keep_first", [(0, 0), (5, 0), (6, 3)])
-def test_sink_attn_scattered_cells_two_sequences(Hh, G, D, V, window, keep_first):
-    """Two sequences share the cell table in shuffled order, with free cells (NaN rows) between; few tokens: the decode form."""
+@pytest.mark.parametrize("n_cells", [96, 2304])
+def test_sink_attn_scattered_cells_two_sequences(Hh, G, D, V, window, keep_first, n_cells):
+    """Two sequences share the cell table in shuffled order, with free cells (NaN rows) between; few tokens: the decode form
+    (with 2304 cells: split over several CTAs per (token, head) and merged)."""
     rng = np.random.default_rng(D + V + window)
-    n_a, n_b, n_cells = 37, 21, 96
+    n_a, n_b = 37, 21
     kc, vc = rng.standard_normal((n_cells, G * D)), rng.standard_normal((n_cells, G * V))
     perm = rng.permutation(n_cells)
     cell_seq, cell_pos = np.full(n_cells, -1), np.full(n_cells, -1)
