@@ -250,25 +250,33 @@ __device__ __forceinline__ unsigned gm_pack_bf2(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const unsigned *>(&v);
 }
-// rows [r0, r0 + n_rows) of an f32 matrix -> bf16 rows of `stride` bytes in shared memory, `width` values kept, the rest of the
-// padded row (pad values) zero; row_of(i) gives the source row or nullptr (a row of zeros)
-template <typename RowOf>
-__device__ __forceinline__ void gm_stage(unsigned char *dst, int stride, int n_rows, int width, int pad, bool vec4, RowOf row_of) {
-    const int per = pad / 4;  // groups of 4 values per row
-    for (int idx = threadIdx.x; idx < n_rows * per; idx += GM_WARPS * 32) {
-        const int r = idx / per, j = (idx - r * per) * 4;
+// ROWS rows of an f32 matrix -> bf16 rows of `stride` bytes in shared memory: `width` values kept, the rest of the padded row
+// (GROUPS groups of 4 values) zero.  row_of(r) gives the source row or nullptr (a row of zeros) and is called by every thread the
+// same number of times (it may exchange values within the warp).  All loads of a thread are issued before the first store, so a
+// tile costs one trip to L2.
+template <int ROWS, int GROUPS, typename RowOf>
+__device__ __forceinline__ void gm_stage(unsigned char *dst, int stride, int width, bool vec4, RowOf row_of) {
+    constexpr int TOTAL = ROWS * GROUPS, TRIPS = (TOTAL + GM_WARPS * 32 - 1) / (GM_WARPS * 32);
+    float4 v[TRIPS];
+#pragma unroll
+    for (int k = 0; k < TRIPS; k++) {
+        const int idx = threadIdx.x + k * GM_WARPS * 32, r = min(idx / GROUPS, ROWS - 1), j = (idx % GROUPS) * 4;
         const float *src = row_of(r);
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (src) {
-            if (vec4 && j + 3 < width) v = *reinterpret_cast<const float4 *>(src + j);
+        v[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (src && idx < TOTAL) {
+            if (vec4 && j + 3 < width) v[k] = *reinterpret_cast<const float4 *>(src + j);
             else {
-                if (j < width) v.x = src[j];
-                if (j + 1 < width) v.y = src[j + 1];
-                if (j + 2 < width) v.z = src[j + 2];
-                if (j + 3 < width) v.w = src[j + 3];
+                if (j < width) v[k].x = src[j];
+                if (j + 1 < width) v[k].y = src[j + 1];
+                if (j + 2 < width) v[k].z = src[j + 2];
+                if (j + 3 < width) v[k].w = src[j + 3];
             }
         }
-        *reinterpret_cast<uint2 *>(dst + r * stride + j * 2) = make_uint2(gm_pack_bf2(v.x, v.y), gm_pack_bf2(v.z, v.w));
+    }
+#pragma unroll
+    for (int k = 0; k < TRIPS; k++) {
+        const int idx = threadIdx.x + k * GM_WARPS * 32, r = idx / GROUPS, j = (idx % GROUPS) * 4;
+        if (idx < TOTAL) *reinterpret_cast<uint2 *>(dst + r * stride + j * 2) = make_uint2(gm_pack_bf2(v[k].x, v[k].y), gm_pack_bf2(v[k].z, v[k].w));
     }
 }
 
@@ -287,7 +295,7 @@ __global__ void __launch_bounds__(GM_WARPS * 32) sink_attn_mma_kernel(const b200
     const bool k4 = D % 4 == 0 && a.k_cache_stride % 4 == 0 && ((uintptr_t)a.k_cache & 15) == 0;
     const bool v4 = V % 4 == 0 && a.v_cache_stride % 4 == 0 && ((uintptr_t)a.v_cache & 15) == 0;
 
-    gm_stage(qs, QSTRIDE, GM_TOK, D, KS * 16, q4, [&](int r) { return t0 + r < a.n_tokens ? a.q + (int64_t)(t0 + r) * a.q_stride + (int64_t)h * D : nullptr; });
+    gm_stage<GM_TOK, KS * 4>(qs, QSTRIDE, D, q4, [&](int r) { return t0 + r < a.n_tokens ? a.q + (int64_t)(t0 + r) * a.q_stride + (int64_t)h * D : nullptr; });
     // the warp's 16 tokens: lane i < 16 holds token i (for the tile test); every lane the two rows of its accumulator fragments
     const int wt = t0 + warp * 16;
     int my_seq = -2, my_pos = 0;
@@ -322,8 +330,9 @@ __global__ void __launch_bounds__(GM_WARPS * 32) sink_attn_mma_kernel(const b200
         const bool warp_sees = __any_sync(0xffffffffu, see);
         if (!__syncthreads_or(warp_sees)) continue;  // (also: the previous tile has been read by every warp)
         if (warp == 0) { cseq[lane] = cs; cpos[lane] = cp; }
-        gm_stage(ks, QSTRIDE, GM_CELLS, D, KS * 16, k4, [&](int r) { return c0 + r < a.n_kv && a.cell_seq[c0 + r] >= 0 ? kb + (int64_t)(c0 + r) * a.k_cache_stride : nullptr; });
-        gm_stage(vs, VSTRIDE, GM_CELLS, V, VS * 16, v4, [&](int r) { return c0 + r < a.n_kv && a.cell_seq[c0 + r] >= 0 ? vb + (int64_t)(c0 + r) * a.v_cache_stride : nullptr; });
+        // lane r of every warp holds cell c0 + r's owner: a row's owner comes by shuffle, not by another load
+        gm_stage<GM_CELLS, KS * 4>(ks, QSTRIDE, D, k4, [&](int r) { return __shfl_sync(0xffffffffu, cs, r) >= 0 ? kb + (int64_t)(c0 + r) * a.k_cache_stride : nullptr; });
+        gm_stage<GM_CELLS, VS * 4>(vs, VSTRIDE, V, v4, [&](int r) { return __shfl_sync(0xffffffffu, cs, r) >= 0 ? vb + (int64_t)(c0 + r) * a.v_cache_stride : nullptr; });
         __syncthreads();
         if (!warp_sees) continue;
         float s[GM_CELLS / 8][4];
