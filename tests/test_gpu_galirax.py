@@ -490,3 +490,58 @@ def test_far_key_through_the_model():
         rows.append(eng.step([("a", [toks[t]], [0])])); places.append(t)
     m.close()
     assert logits_err(np.concatenate(rows), want[places]) < 2e-4
+
+
+# ------------------------------------------------------------------------------------------------ a model folder, the registry, the command line, the trace runner
+def write_model_folder(path, cfg, W):
+    import json
+    import struct
+    meta, blobs, at = {}, [], 0
+    for name, (dt, shape, raw) in R.as_tensors(W).items():
+        b = raw.tobytes()
+        meta[name] = {"dtype": dt, "shape": list(shape), "data_offsets": [at, at + len(b)]}
+        blobs.append(b); at += len(b)
+    head = json.dumps(meta).encode()
+    (path / "model.safetensors").write_bytes(struct.pack("<Q", len(head)) + head + b"".join(blobs))
+    (path / "config.json").write_text(json.dumps(cfg))
+
+
+def test_model_folder_command_line_and_trace_runner(tmp_path, capsys):
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+    from koboldcpp_b200 import __main__ as cli
+    cfg = CONFIGS["mixed"]()
+    W = R.random_weights(cfg, seed=2)
+    write_model_folder(tmp_path, cfg, W)
+    rng = np.random.default_rng(3)
+    pa, pb = rng.integers(0, cfg["vocab"], 9).tolist(), rng.integers(0, cfg["vocab"], 4).tolist()
+    # generate: greedy tokens of two prompts through registry, loader, engine and sampler
+    assert cli.main(["generate", "--model", str(tmp_path), "--dtype", "float32", "--max-new-tokens", "6", "--prompt", ",".join(map(str, pa)), "--prompt", ",".join(map(str, pb))]) == 0
+    lines = [json.loads(x) for x in capsys.readouterr().out.strip().splitlines() if x.startswith("{")]
+    assert [x["prompt"] for x in lines] == [pa, pb]
+    for x in lines:
+        seq = list(x["prompt"])
+        for tok in x["tokens"]:
+            lg = R.forward(cfg, W, seq)[-1]
+            top = np.sort(lg)[-2:]
+            assert tok == int(np.argmax(lg)) or lg[tok] > top[1] - 1e-3 * (abs(top[1]) + 1)
+            seq.append(tok)
+    # the trace runner: two requests start together, decode together, the shorter one ends first
+    ta, tb = rng.integers(0, cfg["vocab"], 14).tolist(), rng.integers(0, cfg["vocab"], 8).tolist()
+    steps = [{"step": 0, "entries": [{"id": "x", "tokens": ta[:11], "want": [0, 10]}, {"id": "y", "tokens": tb[:6], "want": [5]}], "end": []},
+             {"step": 1, "entries": [{"id": "x", "tokens": ta[11:12], "want": []}, {"id": "y", "tokens": tb[6:7], "want": [0]}], "end": []},
+             {"step": 2, "entries": [{"id": "x", "tokens": ta[12:13], "want": [0]}, {"id": "y", "tokens": tb[7:8], "want": [0]}], "end": ["y"]},
+             {"step": 3, "entries": [{"id": "x", "tokens": ta[13:14], "want": [0]}], "end": ["x"]}]
+    out = tmp_path / "out"
+    root = Path(__file__).resolve().parent.parent
+    p = subprocess.run([sys.executable, str(root / "bin" / "trace_run"), "--model", str(tmp_path), "--dtype", "float32", "--out", str(out), "--max-tokens", "64"],
+                       input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [ln for ln in p.stdout.splitlines() if ln.startswith("done")] == ["done 0", "done 1", "done 2", "done 3"]
+    wa, wb = R.forward(cfg, W, ta), R.forward(cfg, W, tb)
+    want = {0: np.stack([wa[0], wa[10], wb[5]]), 1: wb[6:7], 2: np.stack([wa[12], wb[7]]), 3: wa[13:14]}
+    for n, w in want.items():
+        got = np.fromfile(out / f"{n}.f32", dtype="<f4").reshape(-1, cfg["vocab"])
+        assert got.shape == w.shape and logits_err(got, w) < 1e-4, n
