@@ -11,10 +11,10 @@
 // The feed-forward is a mixture of gated experts with a sigmoid router, a choice bias and group-limited choice.  The output is
 // LayerNorm, the head, and a tanh soft cap.
 //
-// Graph choices: everything that reads h and is a matrix -- q, k, v (and the gate), the router -- is ONE product over
-// row-concatenated weights; bias, norm, rotation and the cache store are one launch; the experts of a layer are two stacked
-// tensors (gate over up per expert, and down) used through expert-indexed products; the weighted sum over the chosen experts adds
-// the mixer's result and the residual in the same launch.
+// Graph choices: q, k, v (and the gate) are ONE product over row-concatenated weights; the router is a small f32 product of its
+// own (f32 weights, unrounded input, in every mode); bias, norm, rotation and the cache store are one launch; the experts of a
+// layer are two stacked tensors (gate over up per expert, and down) used through expert-indexed products; the weighted sum over
+// the chosen experts adds the mixer's result and the residual in the same launch.
 #include "host_model.h"
 
 namespace {
@@ -23,7 +23,7 @@ struct GxLayer {
     ggml_tensor *norm1 = nullptr, *norm1b = nullptr, *proj1 = nullptr, *wo = nullptr;
     ggml_tensor *qkvec = nullptr, *sink = nullptr, *freqs = nullptr;     // attention
     ggml_tensor *lnorm = nullptr, *decay = nullptr;                       // lightning
-    ggml_tensor *gate_up = nullptr, *down = nullptr, *correction = nullptr;  // experts
+    ggml_tensor *router = nullptr, *gate_up = nullptr, *down = nullptr, *correction = nullptr;  // experts
 };
 struct GxRun {
     ggml_tensor *k_cache = nullptr, *v_cache = nullptr;  // attention: [kv_heads * dim, n_ctx], [kv_heads * vdim, n_ctx] f32
@@ -50,7 +50,6 @@ int parts_proj1(const b200_layer_params &lp, Part out[8]) {
         out[n++] = {"mix.v", H * V};
         out[n++] = {"mix.g", H * V};
     }
-    if (lp.mlp == B200_MLP_MOE_GATED) out[n++] = {"mlp.router", lp.n_expert};
     return n;
 }
 // the optional vectors of an attention layer, packed in one f32 tensor in this order
@@ -252,6 +251,8 @@ int gx_finalize(b200_llama *m) {
                     LL_REQUIRE(find_w(m, nm), B200_ERR_INVALID, "b200_llama_finalize: tensor %s missing", nm.c_str());
                 }
             GX_NEED(L.gate_up, "mlp.gate_up", W, 2 * (int64_t)lp.ff, lp.n_expert); GX_NEED(L.down, "mlp.down", lp.ff, W, lp.n_expert);
+            GX_NEED(L.router, "mlp.router", W, lp.n_expert);
+            LL_REQUIRE(L.router->type == GGML_TYPE_F32, B200_ERR_INVALID, "b200_llama_finalize: %smlp.router must be uploaded as f32 (the router runs in f32 in every mode)", pre.c_str());
             L.correction = find_w(m, pre + "mlp.correction");
             LL_REQUIRE(!L.correction || L.correction->ne[0] == lp.n_expert, B200_ERR_INVALID, "b200_llama_finalize: %smlp.correction does not fit %d experts", pre.c_str(), lp.n_expert);
         }
@@ -353,7 +354,7 @@ int gx_build(b200_llama *m, const BatchShape &bs) {
             const int64_t F = lp.ff, NU = lp.n_expert_used;
             // the router's result: per token NU weights, then NU expert ids (as i32) in the same row
             ggml_tensor *rt = b.alloc_result(GGML_TYPE_F32, 2 * NU, T);
-            b.ext(rt, B200_EXT_MOE_ROUTE, {part("mlp.router"), L.correction});
+            b.ext(rt, B200_EXT_MOE_ROUTE, {b.mul_mat(L.router, h), L.correction});  // f32 weights times the unrounded h: the choice does not hang on a rounded input
             rt->op_params[2] = lp.n_group < 1 ? 1 : lp.n_group; rt->op_params[3] = lp.n_group_used < 1 ? rt->op_params[2] : lp.n_group_used;
             Builder::set_f(rt, 4, lp.router_scale); rt->op_params[5] = (int32_t)NU;
             ggml_tensor *wts = b.view_2d(rt, NU, T, rt->nb[1], 0), *ids = b.view_2d(rt, NU, T, rt->nb[1], (size_t)NU * 4);

@@ -15,7 +15,7 @@ from pathlib import Path
 
 import numpy as np
 
-from .genesun import SequenceModel, read_safetensors, upload
+from .genesun import SequenceModel, read_safetensors, to_f32, upload
 from .lib import BF16, F32, B200Error
 from .llama import LayerParams
 
@@ -85,7 +85,10 @@ def build(config: dict, tensors, dtype: str = "bfloat16", n_ctx: int = 4096, n_s
                           logit_softcap=float(config.get("logit_softcap") or 0.0), order=run_order(len(layers), config.get("loop")))
     matrix_type = BF16 if dtype == "bfloat16" else F32
     for name, (dt, shape, raw) in tensors.items():
-        upload(model, name, dt, shape, raw, matrix_type)
+        if name.endswith(".mlp.router"):  # the router runs in f32 in both modes
+            model.set_tensor(name, F32, shape, to_f32(dt, raw))
+        else:
+            upload(model, name, dt, shape, raw, matrix_type)
     for il, layer in enumerate(config["layers"]):
         if layer["type"] == "lightning":  # the decays are configuration, the kernel reads them as a tensor
             d = np.asarray(layer["mixer"]["decay"], dtype=np.float32)
