@@ -341,7 +341,9 @@ int gx_build(b200_llama *m, const BatchShape &bs) {
             b.ext(o, B200_EXT_SINK_ATTN, {qo, b.view_2d(R.k_cache, G * D, bs.n_kv, R.k_cache->nb[1], 0), b.view_2d(R.v_cache, G * V, bs.n_kv, R.v_cache->nb[1], 0), L.sink, tok_seq, pos,
                                            cell_seq, cell_pos});
             o->op_params[2] = (int32_t)D; Builder::set_f(o, 3, lp.scale); o->op_params[4] = lp.window; o->op_params[5] = lp.keep_first;
-            o->op_params[6] = L.proj1->type == GGML_TYPE_BF16;  // bf16 weights: the attention products of a prompt batch may be bf16 as well
+            // bf16 weights: the attention products of a prompt batch may be bf16 as well (B200_ATTN_F32=1 keeps them in f32)
+            static const bool attn_f32 = getenv("B200_ATTN_F32") != nullptr;
+            o->op_params[6] = L.proj1->type == GGML_TYPE_BF16 && !attn_f32;
             o->op_params[7] = (int32_t)V;
             y = b.mul_mat(L.wo, o);
         } else {
