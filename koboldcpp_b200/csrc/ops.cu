@@ -632,6 +632,24 @@ __global__ void mul_mat_float_kernel(TD w, TD x, TD dst) {
 }
 
 
+// f32 weights with few outputs and long rows (a router: a handful of rows over the model width): a warp per output would leave one
+// warp to walk a whole row, so a CTA takes an output, its threads 16 bytes at a time, and adds up through shared memory.
+__global__ void __launch_bounds__(128) mul_mat_f32_block_kernel(const float *__restrict__ W, int64_t w_stride, const float *__restrict__ X, int64_t x_stride,
+                                                                float *__restrict__ dst, int64_t dst_stride, int64_t K, bool vec4) {
+    __shared__ float sh[32];
+    const float *wr = W + (int64_t)blockIdx.x * w_stride, *xr = X + (int64_t)blockIdx.y * x_stride;
+    float s = 0.f;
+    if (vec4) {
+        const float4 *w4 = reinterpret_cast<const float4 *>(wr), *x4 = reinterpret_cast<const float4 *>(xr);
+#pragma unroll 4
+        for (int64_t i = threadIdx.x; i < K / 4; i += blockDim.x) { const float4 a = w4[i], b = x4[i]; s += a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w; }
+    } else {
+        for (int64_t i = threadIdx.x; i < K; i += blockDim.x) s += wr[i] * xr[i];
+    }
+    s = block_sum(s, sh);
+    if (threadIdx.x == 0) dst[(int64_t)blockIdx.y * dst_stride + blockIdx.x] = s;
+}
+
 // Dense bf16 weights, 1..8 activation columns (decode): HBM-bound on the weight stream.  A warp owns RPW output rows at a time
 // (two when there are several columns, so an activation value read from L1 meets two weights), 16-byte weight loads that do not
 // allocate in L1 (the activations stay there), f32 activations, f32 accumulation, every column from one read of the row.
@@ -1143,6 +1161,13 @@ extern "C" int b200_op_mul_mat_float(const b200_tensor *w, const b200_tensor *x,
             case 7: launch_gemv_bf16<7>(w, x, dst, st); break;
             default: launch_gemv_bf16<8>(w, x, dst, st); break;
         }
+        B200_CUDA_TRY(cudaGetLastError());
+        return B200_OK;
+    }
+    if (w->type == B200_TYPE_F32 && w->ne[2] == 1 && w->ne[3] == 1 && x->ne[2] == 1 && x->ne[3] == 1 && w->ne[0] >= 512 && w->ne[1] <= 256 && x->ne[1] <= 65535 && dst->nb[0] == 4) {
+        const bool vec4 = w->ne[0] % 4 == 0 && (((uintptr_t)w->data | w->nb[1] | (uintptr_t)x->data | x->nb[1]) & 15) == 0;
+        mul_mat_f32_block_kernel<<<dim3((unsigned)w->ne[1], (unsigned)x->ne[1]), 128, 0, (cudaStream_t)stream>>>((const float *)w->data, (int64_t)(w->nb[1] / 4), (const float *)x->data,
+                                                                                                                (int64_t)(x->nb[1] / 4), (float *)dst->data, (int64_t)(dst->nb[1] / 4), w->ne[0], vec4);
         B200_CUDA_TRY(cudaGetLastError());
         return B200_OK;
     }

@@ -291,6 +291,19 @@ def test_expert_products_bf16_batches_on_the_tensor_cores(K, M, E, top, T):
     assert rel(got, want) < 3e-6
 
 
+@pytest.mark.parametrize("K,M,N", [(4096, 8, 1), (512, 64, 5), (1001, 3, 40), (640, 256, 9), (320, 16, 7)])
+def test_f32_product_with_few_outputs(K, M, N):
+    """Router-shaped products: f32 weights, a handful of rows over the model width (long rows take the CTA-per-output kernel)."""
+    rng = np.random.default_rng(K + M + N)
+    w, x = rng.standard_normal((M, K)).astype(np.float32), rng.standard_normal((N, K + 3)).astype(np.float32)
+    dw, dx, dd = dev(w), dev(x), H.DeviceBuffer(4 * N * (M + 2) + 256)
+    tw, tx, td = Tensor.contiguous(dw.ptr, F32, (K, M)), Tensor.contiguous(dx.ptr, F32, (K, N)), Tensor.contiguous(dd.ptr, F32, (M, N))
+    tx.nb[1], td.nb[1] = 4 * (K + 3), 4 * (M + 2)  # rows of a wider buffer
+    check(lib().b200_op_mul_mat_float(C.byref(tw), C.byref(tx), C.byref(td), None))
+    got = dd.to_numpy(np.float32, (N, M + 2))[:, :M]
+    assert rel(got, x[:, :K].astype(np.float64) @ w.astype(np.float64).T) < 3e-6
+
+
 def test_silu_mul_halves_combine_and_softcap():
     rng = np.random.default_rng(11)
     F, NU, T, Wd = 24, 3, 7, 40
