@@ -25,6 +25,12 @@ MLP_NONE, MLP_MOE_GATED = 0, 2
 ROPE_SCALING_NONE, ROPE_SCALING_BANDS = 0, 2
 
 
+def decays(mx: dict) -> list[float]:
+    """The decay of every head; one number stands for all heads."""
+    d = mx["decay"]
+    return [float(d)] * int(mx["heads"]) if isinstance(d, (int, float)) else [float(x) for x in d]
+
+
 def layer_params(layer: dict) -> LayerParams:
     mx = layer["mixer"]
     lp = LayerParams(kv_from=-1)
@@ -46,7 +52,7 @@ def layer_params(layer: dict) -> LayerParams:
     elif kind == "lightning":
         lp.mixer = MIXER_LIGHTNING
         lp.heads, lp.dim, lp.vdim = int(mx["heads"]), int(mx["dim"]), int(mx["vdim"])
-        if len(mx["decay"]) != lp.heads:
+        if len(decays(mx)) != lp.heads:
             raise B200Error("Galirax: a lightning layer needs one decay per head")
     else:
         raise B200Error(f"Galirax: unknown layer type {kind!r}")
@@ -91,7 +97,7 @@ def build(config: dict, tensors, dtype: str = "bfloat16", n_ctx: int = 4096, n_s
             upload(model, name, dt, shape, raw, matrix_type)
     for il, layer in enumerate(config["layers"]):
         if layer["type"] == "lightning":  # the decays are configuration, the kernel reads them as a tensor
-            d = np.asarray(layer["mixer"]["decay"], dtype=np.float32)
+            d = np.asarray(decays(layer["mixer"]), dtype=np.float32)
             model.set_tensor(f"l{il}.mix.decay", F32, d.shape, d)
     model.finalize()
     return model

@@ -20,6 +20,7 @@ def test_layer_params_from_config():
     assert (b.qkv_bias, b.qk_norm, b.window, b.rope_scaling, b.mlp) == (0, 0, 0, G.ROPE_SCALING_NONE, G.MLP_NONE)
     c = G.layer_params(R.lightning_layer(heads=2, dim=16, vdim=24))
     assert (c.mixer, c.heads, c.dim, c.vdim) == (G.MIXER_LIGHTNING, 2, 16, 24)
+    assert G.decays({"heads": 3, "decay": 0.5}) == [0.5, 0.5, 0.5] and G.decays({"heads": 2, "decay": [0.25, 0.75]}) == [0.25, 0.75]
     with pytest.raises(B200Error):
         G.layer_params({"type": "convolution", "mixer": {}, "mlp": None})
     with pytest.raises(B200Error):
